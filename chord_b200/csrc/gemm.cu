@@ -1,0 +1,340 @@
+// Host side of the W4A16 GEMMs: argument checks, TMA descriptors, launch.
+#include <cuda.h>
+
+#include <mutex>
+#include <unordered_map>
+
+#include "../../include/chord_b200.h"
+#include "common.h"
+#include "w4a16_gemm.cuh"
+
+namespace chord {
+namespace {
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = [] {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult result;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &result) !=
+            cudaSuccess ||
+        result != cudaDriverEntryPointSuccess) {
+      ptr = nullptr;
+    }
+    return reinterpret_cast<EncodeTiledFn>(ptr);
+  }();
+  return fn;
+}
+
+struct MapKey {
+  const void* base;
+  uint64_t dim0, dim1;
+  uint32_t box0, box1;
+  int dtype, swizzle;
+  bool operator==(const MapKey& o) const {
+    return base == o.base && dim0 == o.dim0 && dim1 == o.dim1 && box0 == o.box0 &&
+           box1 == o.box1 && dtype == o.dtype && swizzle == o.swizzle;
+  }
+};
+
+struct MapKeyHash {
+  size_t operator()(const MapKey& k) const {
+    size_t h = reinterpret_cast<size_t>(k.base);
+    auto mix = [&h](uint64_t v) { h ^= v + 0x9e3779b97f4a7c15ull + (h << 6) + (h >> 2); };
+    mix(k.dim0);
+    mix(k.dim1);
+    mix(k.box0);
+    mix(k.box1);
+    mix(static_cast<uint64_t>(k.dtype) * 16 + k.swizzle);
+    return h;
+  }
+};
+
+// Row-major 2-D tensor [dim1 rows, dim0 columns] of 2- or 4-byte elements.
+// Descriptors depend only on (pointer, shape, box), so they are memoised: a
+// decode loop reuses the same weight tensors on every step.
+int make_map_2d(CUtensorMap* out, const void* base, CUtensorMapDataType dtype, uint32_t elem_bytes,
+                uint64_t dim0, uint64_t dim1, uint32_t box0, uint32_t box1,
+                CUtensorMapSwizzle swizzle) {
+  static std::mutex mutex;
+  static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+  const MapKey key{base, dim0, dim1, box0, box1, static_cast<int>(dtype),
+                   static_cast<int>(swizzle)};
+  {
+    std::lock_guard<std::mutex> guard(mutex);
+    auto it = cache.find(key);
+    if (it != cache.end()) {
+      *out = it->second;
+      return kOk;
+    }
+  }
+  EncodeTiledFn encode = encode_tiled_fn();
+  if (encode == nullptr) return fail(kCudaError, "cuTensorMapEncodeTiled is not available");
+  if ((reinterpret_cast<uintptr_t>(base) & 15u) != 0) {
+    return fail(kInvalidArgument, "tensor base address must be 16-byte aligned");
+  }
+  const cuuint64_t dims[2] = {dim0, dim1};
+  const cuuint64_t strides[1] = {dim0 * elem_bytes};
+  const cuuint32_t box[2] = {box0, box1};
+  const cuuint32_t elem_strides[2] = {1, 1};
+  const CUresult rc =
+      encode(out, dtype, 2, const_cast<void*>(base), dims, strides, box, elem_strides,
+             CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (rc != CUDA_SUCCESS) {
+    return fail(kCudaError, "cuTensorMapEncodeTiled failed with CUresult %d (dims %llu x %llu, box %u x %u)",
+                static_cast<int>(rc), static_cast<unsigned long long>(dim0),
+                static_cast<unsigned long long>(dim1), box0, box1);
+  }
+  std::lock_guard<std::mutex> guard(mutex);
+  if (cache.size() > 4096) cache.clear();
+  cache.emplace(key, *out);
+  return kOk;
+}
+
+int grid_size(const DeviceInfo& dev) {
+  const int limit = options().grid_limit;
+  return (limit > 0 && limit < dev.sm_count) ? limit : dev.sm_count;
+}
+
+int round_up16(int64_t v) { return static_cast<int>((v + 15) / 16 * 16); }
+
+size_t fixed_smem_bytes() { return sizeof(GemmShared) + 1024; }
+
+int pick_stages(const DeviceInfo& dev, int mma_n) {
+  const size_t stage = static_cast<size_t>(mma_n) * 128 + kWStageBytes + kSStageBytes;
+  const size_t budget = static_cast<size_t>(dev.max_smem_optin) - fixed_smem_bytes();
+  int stages = static_cast<int>(budget / stage);
+  if (stages > kMaxStages) stages = kMaxStages;
+  const int cap = options().max_stages;
+  if (cap > 0 && stages > cap) stages = cap;
+  return stages;
+}
+
+template <int kGroups>
+int launch_with_groups(const CUtensorMap& tm_w, const CUtensorMap& tm_s, const CUtensorMap& tm_x,
+                       const GemmParams& p, int grid, size_t smem, cudaStream_t stream) {
+  static std::once_flag flags[64];
+  static cudaError_t attr_result[64];
+  int device = 0;
+  CHORD_CUDA(cudaGetDevice(&device));
+  std::call_once(flags[device & 63], [&] {
+    DeviceInfo dev;
+    int max_optin = 227 * 1024;
+    if (current_device_info(&dev) == kOk) max_optin = dev.max_smem_optin;
+    attr_result[device & 63] = cudaFuncSetAttribute(
+        w4a16_gemm_kernel<kGroups>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_optin);
+  });
+  if (attr_result[device & 63] != cudaSuccess) {
+    return fail(kCudaError, "cudaFuncSetAttribute failed: %s",
+                cudaGetErrorString(attr_result[device & 63]));
+  }
+  const int threads = 32 * (8 + 4 * kGroups);
+  w4a16_gemm_kernel<kGroups><<<grid, threads, smem, stream>>>(tm_w, tm_s, tm_x, p);
+  CHORD_CUDA(cudaGetLastError());
+  return kOk;
+}
+
+// Common tail of the three operators: weight/scale/activation descriptors,
+// pipeline depth, scratch checks, launch.
+int launch_gemm(GemmParams p, const void* x, const int32_t* packed, const void* scale,
+                int64_t num_locks, int64_t workspace_bytes, void* stream) {
+  DeviceInfo dev;
+  if (int rc = current_device_info(&dev)) return rc;
+  if (int rc = require_blackwell(dev)) return rc;
+  CHORD_REQUIRE(p.n > 0 && p.n % kBlockN == 0, "N=%d must be a positive multiple of 128", p.n);
+  CHORD_REQUIRE(p.k > 0 && p.k % kBlockK == 0, "K=%d must be a positive multiple of 64", p.k);
+  CHORD_REQUIRE(p.num_experts > 0, "num_experts must be positive");
+  CHORD_REQUIRE(p.tile_tokens > 0 && p.tile_tokens <= kMaxTileTokens,
+                "token tile %d must be in [1, %d]", p.tile_tokens, kMaxTileTokens);
+  CHORD_REQUIRE(x != nullptr && packed != nullptr && scale != nullptr && p.out != nullptr,
+                "null tensor pointer");
+  CHORD_REQUIRE(static_cast<int64_t>(p.num_experts) * (p.k / 16) < (1ll << 31) &&
+                    static_cast<int64_t>(p.x_rows) < (1ll << 31) - 1,
+                "tensor too large for 32-bit TMA coordinates");
+
+  const int grid = grid_size(dev);
+  p.mma_n = round_up16(p.tile_tokens);
+  p.stages = pick_stages(dev, p.mma_n);
+  CHORD_REQUIRE(p.stages >= 2, "token tile %d leaves room for fewer than two pipeline stages",
+                p.tile_tokens);
+  p.x_load = options().x_load;
+  p.num_locks = static_cast<int32_t>(num_locks);
+  CHORD_REQUIRE(p.locks != nullptr && num_locks >= grid,
+                "stream-K needs a zeroed locks buffer of at least %d lock words, got %lld", grid,
+                static_cast<long long>(num_locks));
+  const int64_t need = static_cast<int64_t>(grid) * kBlockN * p.mma_n * 4;
+  CHORD_REQUIRE(p.workspace != nullptr && workspace_bytes >= need,
+                "workspace must hold %lld bytes, got %lld", static_cast<long long>(need),
+                static_cast<long long>(workspace_bytes));
+
+  CUtensorMap tm_w, tm_s, tm_x;
+  if (int rc = make_map_2d(&tm_w, packed, CU_TENSOR_MAP_DATA_TYPE_INT32, 4,
+                           static_cast<uint64_t>(p.n) * 2,
+                           static_cast<uint64_t>(p.num_experts) * (p.k / 16), 256, kBlockK / 16,
+                           CU_TENSOR_MAP_SWIZZLE_NONE))
+    return rc;
+  if (int rc = make_map_2d(&tm_s, scale, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+                           static_cast<uint64_t>(p.n),
+                           static_cast<uint64_t>(p.num_experts) * (p.k / 32), kBlockN,
+                           kBlockK / 32, CU_TENSOR_MAP_SWIZZLE_NONE))
+    return rc;
+  if (int rc = make_map_2d(&tm_x, x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+                           static_cast<uint64_t>(p.k), static_cast<uint64_t>(p.x_rows), 64, 1,
+                           CU_TENSOR_MAP_SWIZZLE_128B))
+    return rc;
+
+  const size_t smem = static_cast<size_t>(p.stages) *
+                          (static_cast<size_t>(p.mma_n) * 128 + kWStageBytes + kSStageBytes) +
+                      fixed_smem_bytes();
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (options().dequant_groups == 4) return launch_with_groups<4>(tm_w, tm_s, tm_x, p, grid, smem, s);
+  return launch_with_groups<2>(tm_w, tm_s, tm_x, p, grid, smem, s);
+}
+
+}  // namespace
+}  // namespace chord
+
+extern "C" {
+
+int chord_b200_indexed_block_m(int64_t n, int64_t k, int64_t num_experts, int64_t routed_m) {
+  (void)n;
+  (void)k;
+  if (num_experts <= 0 || routed_m < 0) return 16;
+  // Rows per local expert if the routes spread evenly; the tile's token
+  // dimension is the MMA N, whose minimum is 16, so smaller blocks buy nothing.
+  const double avg = static_cast<double>(routed_m) / static_cast<double>(num_experts);
+  if (avg <= 8.0) return 16;
+  if (avg <= 20.0) return 32;
+  if (avg <= 44.0) return 64;
+  if (avg <= 100.0) return 128;
+  return 256;
+}
+
+int chord_b200_masked_tile_m(int64_t expected_m) {
+  if (expected_m <= 16) return 16;
+  if (expected_m <= 32) return 32;
+  if (expected_m <= 64) return 64;
+  if (expected_m <= 128) return 128;
+  return 256;
+}
+
+int64_t chord_b200_gemm_workspace_bytes(int64_t tile_tokens) {
+  chord::DeviceInfo dev;
+  if (chord::current_device_info(&dev)) return -1;
+  if (tile_tokens <= 0 || tile_tokens > chord::kMaxTileTokens) {
+    chord::fail(chord::kInvalidArgument, "token tile %lld must be in [1, %d]",
+                static_cast<long long>(tile_tokens), chord::kMaxTileTokens);
+    return -1;
+  }
+  return static_cast<int64_t>(chord::grid_size(dev)) * chord::kBlockN *
+         chord::round_up16(tile_tokens) * 4;
+}
+
+int chord_b200_gemm_lock_words(void) {
+  chord::DeviceInfo dev;
+  if (chord::current_device_info(&dev)) return -1;
+  return chord::grid_size(dev);
+}
+
+int chord_b200_indexed(const void* x, const int32_t* packed, const void* scale,
+                       const int32_t* sorted_ids, int64_t sorted_len, const int32_t* expert_ids,
+                       int64_t expert_len, const int32_t* num_tokens_padded, void* out,
+                       int32_t* locks, int64_t num_locks, void* workspace, int64_t workspace_bytes,
+                       int32_t* status, int64_t m, int64_t n, int64_t k, int64_t num_experts,
+                       int64_t top_k, int64_t block_m, void* stream) {
+  CHORD_REQUIRE(m > 0, "inputs must be non-empty, got m=%lld", static_cast<long long>(m));
+  CHORD_REQUIRE(top_k > 0, "top_k must be positive, got %lld", static_cast<long long>(top_k));
+  CHORD_REQUIRE(block_m > 0 && block_m % 8 == 0 && block_m <= chord::kMaxTileTokens,
+                "routing block_m must be a positive multiple of 8 no larger than %d, got %lld",
+                chord::kMaxTileTokens, static_cast<long long>(block_m));
+  CHORD_REQUIRE(sorted_ids != nullptr && expert_ids != nullptr && num_tokens_padded != nullptr,
+                "null routing pointer");
+  CHORD_REQUIRE(sorted_len >= 0 && expert_len >= 0, "negative routing length");
+  CHORD_REQUIRE(m * top_k < (1ll << 31), "m * top_k overflows int32");
+  chord::GemmParams p{};
+  p.mode = chord::kModeIndexed;
+  p.n = static_cast<int32_t>(n);
+  p.k = static_cast<int32_t>(k);
+  p.num_experts = static_cast<int32_t>(num_experts);
+  p.x_rows = static_cast<int32_t>(m);
+  p.out_rows = static_cast<int32_t>(m * top_k);
+  p.tile_tokens = static_cast<int32_t>(block_m);
+  p.top_k = static_cast<int32_t>(top_k);
+  p.sorted_len = static_cast<int32_t>(sorted_len < (1ll << 30) ? sorted_len : (1ll << 30));
+  p.expert_len = static_cast<int32_t>(expert_len < (1ll << 30) ? expert_len : (1ll << 30));
+  p.sorted_ids = sorted_ids;
+  p.expert_ids = expert_ids;
+  p.num_tokens_padded = num_tokens_padded;
+  p.x = static_cast<const __nv_bfloat16*>(x);
+  p.out = static_cast<__nv_bfloat16*>(out);
+  p.workspace = static_cast<float*>(workspace);
+  p.locks = locks;
+  p.status = status;
+  return chord::launch_gemm(p, x, packed, scale, num_locks, workspace_bytes, stream);
+}
+
+int chord_b200_contiguous(const void* x, const int32_t* packed, const void* scale,
+                          const int32_t* m_indices, void* out, int32_t* locks, int64_t num_locks,
+                          void* workspace, int64_t workspace_bytes, int32_t* status, int64_t m,
+                          int64_t n, int64_t k, int64_t num_experts, void* stream) {
+  CHORD_REQUIRE(m > 0 && m % 128 == 0,
+                "contiguous m=%lld must be a positive multiple of 128 (per-expert padded)",
+                static_cast<long long>(m));
+  CHORD_REQUIRE(m_indices != nullptr, "null m_indices");
+  chord::GemmParams p{};
+  p.mode = chord::kModeContiguous;
+  p.n = static_cast<int32_t>(n);
+  p.k = static_cast<int32_t>(k);
+  p.num_experts = static_cast<int32_t>(num_experts);
+  p.x_rows = static_cast<int32_t>(m);
+  p.out_rows = static_cast<int32_t>(m);
+  p.tile_tokens = 128;
+  p.top_k = 1;
+  p.m_blocks = static_cast<int32_t>(m / 128);
+  p.m_indices = m_indices;
+  p.x = static_cast<const __nv_bfloat16*>(x);
+  p.out = static_cast<__nv_bfloat16*>(out);
+  p.workspace = static_cast<float*>(workspace);
+  p.locks = locks;
+  p.status = status;
+  return chord::launch_gemm(p, x, packed, scale, num_locks, workspace_bytes, stream);
+}
+
+int chord_b200_masked(const void* x, const int32_t* packed, const void* scale,
+                      const int32_t* masked_m, void* out, int32_t* locks, int64_t num_locks,
+                      void* workspace, int64_t workspace_bytes, int32_t* status,
+                      int64_t num_groups, int64_t max_m, int64_t n, int64_t k, int64_t tile_m,
+                      void* stream) {
+  CHORD_REQUIRE(num_groups > 0 && num_groups <= chord::kMaxGroups,
+                "num_groups=%lld must be in [1, %d]", static_cast<long long>(num_groups),
+                chord::kMaxGroups);
+  CHORD_REQUIRE(max_m > 0, "max_m must be positive");
+  CHORD_REQUIRE(masked_m != nullptr, "null masked_m");
+  CHORD_REQUIRE(tile_m > 0 && tile_m <= chord::kMaxTileTokens, "tile_m=%lld must be in [1, %d]",
+                static_cast<long long>(tile_m), chord::kMaxTileTokens);
+  CHORD_REQUIRE(num_groups * max_m < (1ll << 31) - 1, "num_groups * max_m overflows int32");
+  chord::GemmParams p{};
+  p.mode = chord::kModeMasked;
+  p.n = static_cast<int32_t>(n);
+  p.k = static_cast<int32_t>(k);
+  p.num_experts = static_cast<int32_t>(num_groups);
+  p.x_rows = static_cast<int32_t>(num_groups * max_m);
+  p.out_rows = p.x_rows;
+  p.tile_tokens = static_cast<int32_t>(tile_m);
+  p.top_k = 1;
+  p.max_m = static_cast<int32_t>(max_m);
+  p.masked_m = masked_m;
+  p.x = static_cast<const __nv_bfloat16*>(x);
+  p.out = static_cast<__nv_bfloat16*>(out);
+  p.workspace = static_cast<float*>(workspace);
+  p.locks = locks;
+  p.status = status;
+  return chord::launch_gemm(p, x, packed, scale, num_locks, workspace_bytes, stream);
+}
+
+}  // extern "C"

@@ -1,0 +1,156 @@
+/* chord_b200 - C ABI of the B200 (sm_100a) W4A16 MoE GEMM library.
+ *
+ * These are the entry points a binding of the reference library
+ * (novitalabs/chord, package `chord_kernels`) calls in place of its own native
+ * boundary: the torch custom ops `torch.ops.chord.launch_kernel`,
+ * `launch_grouped_w4a16_masked`, `launch_grouped_w4a16_contiguous`
+ * (chord_kernels/operator/csrc/launcher/launcher.cpp:52-158, 459-549, schemas
+ * :605-630) and the repack kernel launch
+ * (chord_kernels/operator/kernel/repack_weight.py:41-77).
+ *
+ * Conventions
+ *  - Every pointer is a device pointer on the current CUDA device unless the
+ *    parameter is documented as host memory.  The caller owns all buffers; the
+ *    library never allocates, frees or synchronises (the single exception is
+ *    chord_b200_repack_w4a16's optional range check, see there).
+ *  - `stream` is a cudaStream_t passed as void*.
+ *  - Functions return 0 on success, 1 for an argument/contract violation
+ *    (bindings raise ValueError), 2 for an unsupported GPU and 3 for a CUDA
+ *    failure (bindings raise RuntimeError).  chord_b200_last_error() returns
+ *    the message of the calling thread's last failure.
+ *  - Entry points are re-entrant and thread-safe.
+ *  - Data formats (bit-exact with the reference):
+ *      packed weight int32 [E, K/16, 2N], scale bf16 [E, K/32, N] as produced
+ *      by pack_w4a16 (chord_kernels/operator/packing.py:55-138,
+ *      include/humming/kernel/repack.cuh:8-121);
+ *      N % 128 == 0, K % 64 == 0.
+ */
+#ifndef CHORD_B200_H_
+#define CHORD_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Message of the calling thread's most recent failure ("" if none). */
+const char* chord_b200_last_error(void);
+
+/* Library build tag, e.g. "chord_b200 sm_100a". */
+const char* chord_b200_version(void);
+
+/* Tuning knobs for sweeps: "x_load" (0 TMA gather4, 1 cp.async),
+ * "dequant_groups" (2 or 4), "max_stages" (0 = auto), "grid_limit" (0 = one
+ * CTA per SM).  Counterpart of the reference's CHORD_W4A16_* environment
+ * overrides (chord_kernels/operator/grouped/heuristics.py:32-39).  Process-wide. */
+int chord_b200_set_option(const char* name, int64_t value);
+
+/* ---- packing: replaces repack_w4a16<kPacked> (repack.cuh:48-121) ----------
+ * in : packed_input == 0: int32 codes [E, N, K], each in [0, 15];
+ *      packed_input == 1: checkpoint words int32 [E, N, K/8], eight
+ *      little-endian nibbles per word.
+ * out: int32 [E, K/16, 2N].
+ * range_flag: optional int32 device word; the kernel ORs 1 into it when a
+ *      code lies outside [0, 15] (unpacked input only).  The reference checks
+ *      this range on the host with torch.aminmax (packing.py:111-117). */
+int chord_b200_repack_w4a16(const int32_t* in, int32_t* out, int64_t num_experts, int64_t n,
+                            int64_t k, int packed_input, int32_t* range_flag, void* stream);
+
+/* Replaces _pack_weight_scale (packing.py:45-52): bf16 [E, N, K/32] ->
+ * bf16 [E, K/32, N] with out[e, g, 64c + j] = in[e, 64c + 8*(j%8) + j/8, g]. */
+int chord_b200_permute_scale(const void* in, void* out, int64_t num_experts, int64_t n, int64_t k,
+                             void* stream);
+
+/* ---- schedule queries ------------------------------------------------------
+ * Routing block size for `indexed` (replaces indexed_block_m /
+ * select_indexed_config(...).block_m, chord_kernels/operator/api.py:300-315,
+ * tuning.py:512-554).  Always a multiple of 8. */
+int chord_b200_indexed_block_m(int64_t n, int64_t k, int64_t num_experts, int64_t routed_m);
+
+/* Token-tile size the masked kernel uses for `expected_m` (replaces
+ * _w4a16_masked_bm, chord_kernels/operator/grouped/heuristics.py:58-72). */
+int chord_b200_masked_tile_m(int64_t expected_m);
+
+/* Bytes of FP32 stream-K scratch a GEMM launch with this token tile needs on
+ * the current device (the reference allocates it per launch inside its
+ * launcher, launcher.cpp:110-123).  Returns < 0 on error. */
+int64_t chord_b200_gemm_workspace_bytes(int64_t tile_tokens);
+
+/* Lock words a GEMM launch touches on the current device (all left zero).
+ * The reference needs grid + grid/10 (launcher.cpp:95-109). */
+int chord_b200_gemm_lock_words(void);
+
+/* ---- indexed GEMM: replaces launch_kernel (launcher.cpp:52-158) -------------
+ * out[id, :] = x[id / top_k, :] . dequant(W[expert_ids[block of id]])^T for every
+ * id < m * top_k found in sorted_ids[0 .. *num_tokens_padded).
+ *  x                 bf16 [m, k]
+ *  sorted_ids        int32 [sorted_len]; blocks of block_m ids, valid prefix then sentinels
+ *  expert_ids        int32 [expert_len]; expert of each block
+ *  num_tokens_padded int32 [1], read on the device
+ *  out               bf16 [m * top_k, n]; rows no id names are left untouched
+ *  locks             int32 [num_locks] all zero on entry, all zero on exit
+ *  workspace         FP32 scratch of chord_b200_gemm_workspace_bytes(block_m)
+ *  status            optional int32 word; a kernel that gives up on a bounded
+ *                    wait ORs a nonzero code into it instead of hanging
+ *  block_m           multiple of 8, at most 256 */
+int chord_b200_indexed(const void* x, const int32_t* packed, const void* scale,
+                       const int32_t* sorted_ids, int64_t sorted_len, const int32_t* expert_ids,
+                       int64_t expert_len, const int32_t* num_tokens_padded, void* out,
+                       int32_t* locks, int64_t num_locks, void* workspace, int64_t workspace_bytes,
+                       int32_t* status, int64_t m, int64_t n, int64_t k, int64_t num_experts,
+                       int64_t top_k, int64_t block_m, void* stream);
+
+/* ---- contiguous GEMM: replaces launch_grouped_w4a16_contiguous
+ * (launcher.cpp:505-549) --------------------------------------------------------
+ * out[r, :] = x[r, :] . dequant(W[m_indices[tile first row]])^T for every 128-row
+ * tile whose first row has m_indices >= 0; other tiles are left untouched.
+ *  x bf16 [m, k], m % 128 == 0; m_indices int32 [m]; out bf16 [m, n]. */
+int chord_b200_contiguous(const void* x, const int32_t* packed, const void* scale,
+                          const int32_t* m_indices, void* out, int32_t* locks, int64_t num_locks,
+                          void* workspace, int64_t workspace_bytes, int32_t* status, int64_t m,
+                          int64_t n, int64_t k, int64_t num_experts, void* stream);
+
+/* ---- masked GEMM: replaces launch_grouped_w4a16_masked (launcher.cpp:459-503) --
+ * out[g, r, :] = x[g, r, :] . dequant(W[g])^T for r < masked_m[g]; other rows are
+ * left untouched.
+ *  x bf16 [num_groups, max_m, k]; masked_m int32 [num_groups];
+ *  out bf16 [num_groups, max_m, n]; tile_m from chord_b200_masked_tile_m(). */
+int chord_b200_masked(const void* x, const int32_t* packed, const void* scale,
+                      const int32_t* masked_m, void* out, int32_t* locks, int64_t num_locks,
+                      void* workspace, int64_t workspace_bytes, int32_t* status,
+                      int64_t num_groups, int64_t max_m, int64_t n, int64_t k, int64_t tile_m,
+                      void* stream);
+
+/* ---- SiLU * mul between gate_up and down --------------------------------------
+ * out[r, j] = silu(in[r, j]) * in[r, inter + j], in bf16 [rows, 2*inter], out bf16
+ * [rows, inter].  The reference leaves this step to its caller; the gate-first
+ * column order is the fused-w13 convention its shapes assume
+ * (tests/generators.py:419-420). */
+int chord_b200_silu_mul(const void* in, void* out, int64_t rows, int64_t inter, void* stream);
+
+/* Same, but only for the rows named by the valid ids (< row_limit) among
+ * sorted_ids[0 .. *num_tokens_padded): the rows `indexed` wrote. */
+int chord_b200_silu_mul_routed(const void* in, void* out, const int32_t* sorted_ids,
+                               int64_t sorted_len, const int32_t* num_tokens_padded,
+                               int64_t row_limit, int64_t inter, void* stream);
+
+/* ---- routing alignment (moe_align_block_size) -----------------------------------
+ * CUDA form of the reference's align_routing_blocks (tests/generators.py:192-230):
+ * topk_ids int32 [numel] holds global expert ids; routes to experts in
+ * [expert_base, expert_base + num_experts) are sorted by expert (ids ascending
+ * inside an expert) into blocks of block_m, padded with the sentinel `numel`.
+ * Experts without routes emit no block.
+ *  sorted_ids int32 [sorted_cap], expert_ids int32 [expert_cap] (local expert
+ *  index), num_tokens_padded int32 [1].  Capacities must cover the worst case
+ *  numel + num_experts * (block_m - 1) ids. */
+int chord_b200_moe_align_block_size(const int32_t* topk_ids, int64_t numel, int64_t expert_base,
+                                    int64_t num_experts, int64_t block_m, int32_t* sorted_ids,
+                                    int64_t sorted_cap, int32_t* expert_ids, int64_t expert_cap,
+                                    int32_t* num_tokens_padded, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* CHORD_B200_H_ */
