@@ -18,14 +18,14 @@ __all__ = [
 ]
 
 _EXPORTS = {
-    "indexed": "chord_b200.indexed",
-    "indexed_block_m": "chord_b200.indexed",
-    "masked": "chord_b200.grouped",
-    "contiguous": "chord_b200.grouped",
+    "indexed": "chord_b200.indexed_gemm",
+    "indexed_block_m": "chord_b200.indexed_gemm",
+    "masked": "chord_b200.grouped_gemm",
+    "contiguous": "chord_b200.grouped_gemm",
     "pack_w4a16": "chord_b200.packing",
     "PreparedWeight": "chord_b200.packing",
-    "silu_mul": "chord_b200.fused",
-    "moe_align_block_size": "chord_b200.fused",
+    "silu_mul": "chord_b200.fused_ops",
+    "moe_align_block_size": "chord_b200.fused_ops",
 }
 
 

@@ -83,7 +83,7 @@ def _apply_env_options(lib: ctypes.CDLL) -> None:
         if value is None:
             continue
         if option == "x_load" and not value.isdigit():
-            value = {"gather4": "0", "cpasync": "1"}[value]
+            value = {"cpasync": "0", "gather4": "1"}[value]
         check(lib.chord_b200_set_option(option.encode(), int(value)))
 
 

@@ -61,10 +61,13 @@ int require_blackwell(const DeviceInfo& info);
 
 // Tuning knobs settable through chord_b200_set_option().
 struct Options {
-  int x_load = 0;          // 0 = TMA gather4, 1 = cp.async
+  int x_load = 0;          // indexed activation gather: 0 = cp.async helper warps, 1 = TMA gather4
   int dequant_groups = 2;  // 2 or 4 groups of four dequant warps
+  int issuers = 0;         // 0 = automatic; 1, 2 or 4 MMA issuers
   int max_stages = 0;      // 0 = as many as fit
   int grid_limit = 0;      // 0 = one CTA per SM
+  int ablate = 0;          // CHORD_PROFILE builds: bit mask of work to skip in timing studies
+  long long profile_buffer = 0;  // device pointer for per-CTA cycle counters (CHORD_PROFILE builds)
 };
 Options& options();
 

@@ -70,12 +70,20 @@ int chord_b200_set_option(const char* name, int64_t value) {
   } else if (!std::strcmp(name, "dequant_groups")) {
     if (value != 2 && value != 4) return fail(kInvalidArgument, "dequant_groups must be 2 or 4");
     o.dequant_groups = static_cast<int>(value);
+  } else if (!std::strcmp(name, "issuers")) {
+    if (value != 0 && value != 1 && value != 2 && value != 4)
+      return fail(kInvalidArgument, "issuers must be 0, 1, 2 or 4");
+    o.issuers = static_cast<int>(value);
   } else if (!std::strcmp(name, "max_stages")) {
     if (value < 0 || value > 64) return fail(kInvalidArgument, "max_stages must be in [0, 64]");
     o.max_stages = static_cast<int>(value);
   } else if (!std::strcmp(name, "grid_limit")) {
     if (value < 0) return fail(kInvalidArgument, "grid_limit must be >= 0");
     o.grid_limit = static_cast<int>(value);
+  } else if (!std::strcmp(name, "ablate")) {
+    o.ablate = static_cast<int>(value);
+  } else if (!std::strcmp(name, "profile_buffer")) {
+    o.profile_buffer = static_cast<long long>(value);
   } else {
     return fail(kInvalidArgument, "unknown option '%s'", name);
   }

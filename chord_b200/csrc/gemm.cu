@@ -105,13 +105,26 @@ int round_up16(int64_t v) { return static_cast<int>((v + 15) / 16 * 16); }
 
 size_t fixed_smem_bytes() { return sizeof(GemmShared) + 1024; }
 
-int pick_stages(const DeviceInfo& dev, int mma_n) {
-  const size_t stage = static_cast<size_t>(mma_n) * 128 + kWStageBytes + kSStageBytes;
-  const size_t budget = static_cast<size_t>(dev.max_smem_optin) - fixed_smem_bytes();
-  int stages = static_cast<int>(budget / stage);
-  if (stages > kMaxStages) stages = kMaxStages;
+size_t x_stage_bytes(int mma_n) { return static_cast<size_t>(mma_n) * 256; }
+
+// Depth of the activation ring: small tiles get a deep ring cheaply, large
+// ones are limited to what leaves room for the weight ring.
+int pick_x_stages(int mma_n) {
+  int stages = mma_n <= 32 ? 8 : mma_n <= 64 ? 6 : mma_n <= 128 ? 3 : 2;
   const int cap = options().max_stages;
-  if (cap > 0 && stages > cap) stages = cap;
+  if (cap > 0 && stages > cap) stages = cap < 2 ? 2 : cap;
+  return stages;
+}
+
+// The weight/scale ring takes the rest of shared memory.
+int pick_w_stages(const DeviceInfo& dev, int mma_n, int x_stages) {
+  const size_t used = fixed_smem_bytes() + static_cast<size_t>(x_stages) * x_stage_bytes(mma_n);
+  if (used >= static_cast<size_t>(dev.max_smem_optin)) return 0;
+  const size_t budget = static_cast<size_t>(dev.max_smem_optin) - used;
+  int stages = static_cast<int>(budget / (kWStageBytes + kSStageBytes));
+  if (stages > kMaxWStages) stages = kMaxWStages;
+  const int cap = options().max_stages;
+  if (cap > 0 && stages > cap) stages = cap < 2 ? 2 : cap;
   return stages;
 }
 
@@ -133,7 +146,7 @@ int launch_with_groups(const CUtensorMap& tm_w, const CUtensorMap& tm_s, const C
     return fail(kCudaError, "cudaFuncSetAttribute failed: %s",
                 cudaGetErrorString(attr_result[device & 63]));
   }
-  const int threads = 32 * (8 + 4 * kGroups);
+  const int threads = 32 * (12 + 4 * kGroups);
   w4a16_gemm_kernel<kGroups><<<grid, threads, smem, stream>>>(tm_w, tm_s, tm_x, p);
   CHORD_CUDA(cudaGetLastError());
   return kOk;
@@ -147,7 +160,7 @@ int launch_gemm(GemmParams p, const void* x, const int32_t* packed, const void* 
   if (int rc = current_device_info(&dev)) return rc;
   if (int rc = require_blackwell(dev)) return rc;
   CHORD_REQUIRE(p.n > 0 && p.n % kBlockN == 0, "N=%d must be a positive multiple of 128", p.n);
-  CHORD_REQUIRE(p.k > 0 && p.k % kBlockK == 0, "K=%d must be a positive multiple of 64", p.k);
+  CHORD_REQUIRE(p.k > 0 && p.k % 64 == 0, "K=%d must be a positive multiple of 64", p.k);
   CHORD_REQUIRE(p.num_experts > 0, "num_experts must be positive");
   CHORD_REQUIRE(p.tile_tokens > 0 && p.tile_tokens <= kMaxTileTokens,
                 "token tile %d must be in [1, %d]", p.tile_tokens, kMaxTileTokens);
@@ -157,12 +170,24 @@ int launch_gemm(GemmParams p, const void* x, const int32_t* packed, const void* 
                     static_cast<int64_t>(p.x_rows) < (1ll << 31) - 1,
                 "tensor too large for 32-bit TMA coordinates");
 
+  CHORD_REQUIRE(static_cast<int64_t>(p.x_rows) * p.k < (1ll << 31),
+                "activation tensor too large for 32-bit element offsets");
   const int grid = grid_size(dev);
   p.mma_n = round_up16(p.tile_tokens);
-  p.stages = pick_stages(dev, p.mma_n);
-  CHORD_REQUIRE(p.stages >= 2, "token tile %d leaves room for fewer than two pipeline stages",
+  p.x_stages = pick_x_stages(p.mma_n);
+  p.w_stages = pick_w_stages(dev, p.mma_n, p.x_stages);
+  CHORD_REQUIRE(p.w_stages >= 2, "token tile %d leaves room for fewer than two pipeline stages",
                 p.tile_tokens);
-  p.x_load = options().x_load;
+  // Consecutive rows take one tiled box per K half; routed rows are gathered.
+  // Small token tiles are issue-bound with one MMA issuer: use one per dequant group.
+  const int groups = options().dequant_groups == 4 ? 4 : 2;
+  // Keep the accumulators double-buffered (2 * issuers * mma_n <= 256 columns) where possible.
+  p.issuers = p.mma_n <= 32 ? groups : (p.mma_n <= 64 ? 2 : 1);
+  if (options().issuers > 0 && options().issuers * p.mma_n <= 256) p.issuers = options().issuers;
+  p.x_load = p.mode == kModeIndexed ? (options().x_load == 1 ? kXLoadGather4 : kXLoadCpAsync)
+                                    : kXLoadTiled;
+  p.profile = reinterpret_cast<unsigned long long*>(options().profile_buffer);
+  p.ablate = options().ablate;
   p.num_locks = static_cast<int32_t>(num_locks);
   CHORD_REQUIRE(p.locks != nullptr && num_locks >= grid,
                 "stream-K needs a zeroed locks buffer of at least %d lock words, got %lld", grid,
@@ -184,12 +209,13 @@ int launch_gemm(GemmParams p, const void* x, const int32_t* packed, const void* 
                            kBlockK / 32, CU_TENSOR_MAP_SWIZZLE_NONE))
     return rc;
   if (int rc = make_map_2d(&tm_x, x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
-                           static_cast<uint64_t>(p.k), static_cast<uint64_t>(p.x_rows), 64, 1,
+                           static_cast<uint64_t>(p.k), static_cast<uint64_t>(p.x_rows), 64,
+                           p.x_load == kXLoadTiled ? static_cast<uint32_t>(p.mma_n) : 1u,
                            CU_TENSOR_MAP_SWIZZLE_128B))
     return rc;
 
-  const size_t smem = static_cast<size_t>(p.stages) *
-                          (static_cast<size_t>(p.mma_n) * 128 + kWStageBytes + kSStageBytes) +
+  const size_t smem = static_cast<size_t>(p.x_stages) * x_stage_bytes(p.mma_n) +
+                      static_cast<size_t>(p.w_stages) * (kWStageBytes + kSStageBytes) +
                       fixed_smem_bytes();
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (options().dequant_groups == 4) return launch_with_groups<4>(tm_w, tm_s, tm_x, p, grid, smem, s);

@@ -60,42 +60,41 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t byt
                : "memory");
 }
 
+// One try: returns at once if the phase has completed, otherwise the hardware may
+// park the warp until it completes or the suspend-time hint (nanoseconds) runs out.
+// Parked warps take no issue slots, which matters here: some twenty warps per CTA
+// wait on barriers most of the time, and a hot spin would crowd out the few warps
+// that issue TMA, MMA and dequantisation instructions.
+constexpr uint32_t kSuspendHintNs = 200000;
+
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t done;
   asm volatile(
       "{\n\t"
       ".reg .pred P;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 P, [%1], %2;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 P, [%1], %2, %3;\n\t"
       "selp.u32 %0, 1, 0, P;\n\t"
       "}\n"
       : "=r"(done)
-      : "r"(bar), "r"(parity)
+      : "r"(bar), "r"(parity), "r"(kSuspendHintNs)
       : "memory");
   return done != 0;
 }
 
 // Bounded wait.  `abort_flag` is a shared-memory word any role may set when it
 // gives up; once set, every other waiter leaves too.  Returns false on
-// timeout (two seconds of wall clock) or abort.
-constexpr uint64_t kWaitTimeoutNs = 2000000000ull;
-
-__device__ __forceinline__ uint64_t global_timer_ns() {
-  uint64_t t;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-  return t;
-}
+// timeout (about two seconds of SM clock) or abort.
+constexpr long long kWaitTimeoutCycles = 4000000000ll;
 
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity,
                                           volatile uint32_t* abort_flag) {
   if (mbar_try_wait(bar, parity)) return true;
-  uint64_t start = 0;
+  const long long start = clock64();
   for (uint32_t spin = 1;; ++spin) {
     if (mbar_try_wait(bar, parity)) return true;
-    if ((spin & 0x3f) == 0) {
+    if ((spin & 0x3) == 0) {
       if (*abort_flag != 0) return false;
-      const uint64_t now = global_timer_ns();
-      if (start == 0) start = now;
-      else if (now - start > kWaitTimeoutNs) return false;
+      if (clock64() - start > kWaitTimeoutCycles) return false;
     }
   }
 }
@@ -160,8 +159,24 @@ __device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src, bool 
                : "memory");
 }
 
+// Deferred arrival: counts toward the barrier's expected arrivals (no pending-count
+// increment) and fires when all cp.async issued so far by this thread have completed.
+__device__ __forceinline__ void cp_async_arrive_noinc(uint32_t bar) {
+  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
+}
+
 __device__ __forceinline__ void cp_async_wait_all() {
   asm volatile("cp.async.wait_all;" ::: "memory");
+}
+
+__device__ __forceinline__ void cp_async_commit() {
+  asm volatile("cp.async.commit_group;" ::: "memory");
+}
+
+// Returns once at most kPending of this thread's committed groups are still in flight.
+template <int kPending>
+__device__ __forceinline__ void cp_async_wait_group() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(kPending) : "memory");
 }
 
 // ----------------------------------------------------------------- tcgen05 --

@@ -14,17 +14,38 @@
 // warps read the packed words the TMA brought in, expand them to BF16 in
 // registers and store them straight into tensor memory, from where
 // tcgen05.mma takes its A operand.  Activations arrive K-major with the
-// 128-byte swizzle, either by TMA tile::gather4 (four arbitrary rows per
-// instruction - the routed-row gather) or, as a selectable variant, by
-// per-thread cp.async.
+// 128-byte swizzle: one tiled TMA box per K half where a tile's rows are
+// consecutive, a cp.async gather by two helper warps (or, selectable, TMA
+// tile::gather4) where sorted_ids names them.
+//
+// Two shared-memory rings decouple the HBM stream from the token side: a
+// weight/scale stage is free again as soon as the dequant warps have read it
+// into registers (its content lives on in tensor memory), so that ring can be
+// deep enough (20+ stages of 9 KB) to cover HBM latency, while an activation
+// stage stays until the MMAs that read it have completed.
+//
+// The single-thread issue loops (TMA, MMA) are kept free of divisions and
+// descriptor rebuilds: one lone thread retires a dependent instruction only
+// every few cycles, and at decode sizes a K16 MMA has roughly 45 cycles of HBM
+// time to hide behind.
 //
 // Warp roles (one CTA per SM, persistent):
-//   warp 0            producer: TMA for packed weights, scales, activations
-//   warp 1            MMA issuer (one thread)
-//   warp 2            tensor-memory allocator
-//   warps 4..4+4G-1   G dequant groups of four warps (one per TMEM lane quarter)
+//   warp 0            producer: TMA for packed weights
+//   warp 1            producer: TMA for scales
+//   warps 2-3         activations: tiled TMA (one thread), cp.async gather (64 threads)
+//                     or TMA gather4 (one warp); warp 2 also allocates tensor memory
+//   warps 4-7         MMA issuers, one thread each; issuer i takes the stages
+//                     with index = i modulo the issuer count and owns one accumulator
+//   warps 8..8+4G-1   G dequant groups of four warps (one per TMEM lane quarter)
 //   last four warps   epilogue: TMEM -> registers -> BF16 -> global, plus the
 //                     stream-K reduction through `locks` and the FP32 workspace
+//
+// Why several issuers: one thread can issue a tcgen05.mma only every ~56 cycles
+// (measured), while a 128x16 tile of packed weights arrives from HBM every ~45
+// cycles per SM.  With small token tiles (decode) the stages are therefore
+// dealt to 2 or 4 issuers in different warps, each accumulating into its own
+// TMEM columns; the epilogue adds the accumulators in issuer order, so the
+// result does not depend on timing.  Large token tiles use a single issuer.
 //
 // Scheduling follows the reference's scheme (humming/scheduler.cuh:73-101):
 // whole tiles are dealt round-robin to the CTAs while full waves last; the
@@ -44,10 +65,35 @@
 
 #include "ptx.cuh"
 
+#ifdef CHORD_PROFILE
+#define CHORD_ABLATE(bit) ((p.ablate >> (bit)) & 1)
+#define CHORD_PROF_INIT() long long prof_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0}; const long long prof_start = clock64()
+#define CHORD_PROF_T(var) const long long var = clock64()
+#define CHORD_PROF_ADD(i, var) prof_acc[i] += clock64() - var
+#define CHORD_PROF_FLUSH(role)                                                         \
+  do {                                                                                 \
+    if (p.profile != nullptr && lane == 0) {                                           \
+      prof_acc[0] = clock64() - prof_start;                                            \
+      for (int pi = 0; pi < 8; ++pi)                                                   \
+        p.profile[(blockIdx.x * 8 + (role)) * 8 + pi] = static_cast<unsigned long long>(prof_acc[pi]); \
+    }                                                                                  \
+  } while (0)
+#else
+#define CHORD_ABLATE(bit) 0
+#define CHORD_PROF_INIT() do {} while (0)
+#define CHORD_PROF_T(var) do {} while (0)
+#define CHORD_PROF_ADD(i, var) do {} while (0)
+#define CHORD_PROF_FLUSH(role) do {} while (0)
+#endif
+
 namespace chord {
 
 enum GemmMode : int32_t { kModeIndexed = 0, kModeContiguous = 1, kModeMasked = 2 };
-enum XLoadMode : int32_t { kXLoadGather4 = 0, kXLoadCpAsync = 1 };
+// How activation rows reach shared memory.  Consecutive rows (contiguous,
+// masked) always use one tiled TMA box per 64-wide K half; the routed rows of
+// `indexed` are gathered by two helper warps with cp.async (default) or by the
+// producer with TMA tile::gather4.
+enum XLoadMode : int32_t { kXLoadCpAsync = 0, kXLoadGather4 = 1, kXLoadTiled = 2 };
 
 // Device status bits (OR-ed into *status by a kernel that gave up on a wait).
 enum StatusBits : int32_t {
@@ -59,14 +105,20 @@ enum StatusBits : int32_t {
 };
 
 constexpr int kBlockN = 128;      // weight rows per tile (MMA M)
-constexpr int kBlockK = 64;       // K elements per pipeline stage
-constexpr int kMaxStages = 12;
-constexpr int kASlots = 4;        // tensor-memory ring for the dequantised A operand
-constexpr int kAColsPerSlot = kBlockK / 2;
-constexpr int kDCol0 = kASlots * kAColsPerSlot;  // 128
+constexpr int kBlockK = 128;      // K elements per pipeline stage (two 64-wide swizzle atoms)
+constexpr int kMaxWStages = 24;   // ring of packed-weight + scale stages
+constexpr int kMaxXStages = 8;    // ring of activation stages
+// Tensor-memory ring for the dequantised A operand: eight slots of one 64-wide K
+// half (32 columns) each.  Stage `it` uses slots 2 (it % 4) and 2 (it % 4) + 1, so
+// that the MMAs of a stage's first half are issued while its second half is still
+// being dequantised.
+constexpr int kASlots = 8;
+constexpr int kAColsPerSlot = 32;
+constexpr int kDCol0 = kASlots * kAColsPerSlot;  // 256
+constexpr int kHelperThreads = 64;  // warps 2-3: activation gather for `indexed`
 constexpr int kTmemCols = 512;
 constexpr int kMaxTileTokens = 256;
-constexpr int kMaxGroups = 1024;  // masked: prefix table capacity
+constexpr int kMaxGroups = 512;   // masked: prefix table capacity
 constexpr int kWStageBytes = (kBlockK / 16) * 1024;
 constexpr int kSStageBytes = (kBlockK / 32) * 256;
 
@@ -85,7 +137,9 @@ struct GemmParams {
   int32_t m_blocks;     // contiguous: m / 128
   int32_t sorted_len;   // indexed: capacity of sorted_ids
   int32_t expert_len;   // indexed: capacity of expert_ids
-  int32_t stages;
+  int32_t w_stages;     // depth of the weight/scale ring
+  int32_t x_stages;     // depth of the activation ring
+  int32_t issuers;      // 1, 2 or 4 MMA issuers (and accumulators)
   int32_t num_locks;
   const int32_t* sorted_ids;
   const int32_t* expert_ids;
@@ -97,6 +151,8 @@ struct GemmParams {
   float* workspace;     // grid * 128 * mma_n floats
   int32_t* locks;
   int32_t* status;
+  unsigned long long* profile;  // CHORD_PROFILE builds only: per-CTA cycle counters
+  int32_t ablate;               // CHORD_PROFILE builds only: skip parts of the work (timing studies)
 };
 
 struct TileInfo {
@@ -186,8 +242,10 @@ struct SegmentIterator {
 };
 
 struct __align__(16) GemmShared {
-  uint64_t full[kMaxStages];
-  uint64_t empty[kMaxStages];
+  uint64_t wfull[kMaxWStages];   // weights + scales landed        (2 producer arrivals + bytes)
+  uint64_t wempty[kMaxWStages];  // dequant warps have read them   (4 arrivals)
+  uint64_t xfull[kMaxXStages];   // activations landed
+  uint64_t xempty[kMaxXStages];  // the stage's MMAs have completed (1 commit)
   uint64_t afull[kASlots];
   uint64_t aempty[kASlots];
   uint64_t dfull[2];
@@ -196,6 +254,7 @@ struct __align__(16) GemmShared {
   uint32_t abort_flag;
   int32_t m_blocks;
   volatile uint32_t epilogue_failed;
+  int32_t x_slots;                   // helpers: token slots of the current tile that carry a row
   int32_t out_row[kMaxTileTokens];   // epilogue: output row per token slot, -1 = skip
   int32_t x_row[kMaxTileTokens];     // producer (cp.async variant): activation row per slot
   int32_t group_prefix[kMaxGroups + 1];  // masked: first M tile of each group
@@ -293,46 +352,72 @@ __device__ __forceinline__ void dequant_word(uint32_t w, uint32_t scale_lo, uint
   out[3] = bf16x2_mul(bf16x2_sub(v3, kBias), scale_hi);  // rows r+8, K-half 1
 }
 
+// Ring position advanced without divisions (a lone issuing thread pays ~100
+// cycles for an integer division by a runtime value).
+struct StageCursor {
+  uint32_t s = 0, ph = 0;
+  __device__ __forceinline__ void advance(uint32_t stages) {
+    if (++s == stages) {
+      s = 0;
+      ph ^= 1u;
+    }
+  }
+};
+
 template <int kDequantGroups>
-__global__ void __launch_bounds__(32 * (8 + 4 * kDequantGroups), 1)
+__global__ void __launch_bounds__(32 * (12 + 4 * kDequantGroups), 1)
 w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_s,
                   const __grid_constant__ CUtensorMap tm_x, const GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
-  // Dynamic shared memory: [X stages | W stages | S stages | GemmShared], 1024-aligned.
+  // Dynamic shared memory: [X ring | W ring | S ring | GemmShared], 1024-aligned.
+  // One X stage holds two K halves, each mma_n rows of 128 bytes.
   const uint32_t raw_addr = ptx::smem_u32(smem_raw);
   const uint32_t pad = (1024u - (raw_addr & 1023u)) & 1023u;
   uint8_t* smem = smem_raw + pad;
-  const uint32_t x_stage_bytes = static_cast<uint32_t>(p.mma_n) * 128u;
-  const uint32_t stages = static_cast<uint32_t>(p.stages);
+  const uint32_t x_half_bytes = static_cast<uint32_t>(p.mma_n) * 128u;
+  const uint32_t x_stage_bytes = 2u * x_half_bytes;
+  const uint32_t w_stages = static_cast<uint32_t>(p.w_stages);
+  const uint32_t x_stages = static_cast<uint32_t>(p.x_stages);
   uint8_t* smem_x = smem;
-  uint8_t* smem_w = smem_x + stages * x_stage_bytes;
-  uint8_t* smem_s = smem_w + stages * kWStageBytes;
-  GemmShared& sh = *reinterpret_cast<GemmShared*>(smem_s + stages * kSStageBytes);
+  uint8_t* smem_w = smem_x + x_stages * x_stage_bytes;
+  uint8_t* smem_s = smem_w + w_stages * kWStageBytes;
+  GemmShared& sh = *reinterpret_cast<GemmShared*>(smem_s + w_stages * kSStageBytes);
 
   const uint32_t warp = threadIdx.x >> 5;
   const uint32_t lane = threadIdx.x & 31;
-  constexpr uint32_t kFirstDequantWarp = 4;
-  constexpr uint32_t kFirstEpilogueWarp = 4 + 4 * kDequantGroups;
-  const uint32_t d_bufs = p.mma_n <= 128 ? 2u : 1u;
-  const uint32_t d_stride = p.mma_n <= 128 ? 128u : 256u;
-  const int32_t k_iters = p.k / kBlockK;
+  constexpr uint32_t kFirstIssuerWarp = 4;
+  constexpr uint32_t kFirstDequantWarp = 8;
+  constexpr uint32_t kFirstEpilogueWarp = 8 + 4 * kDequantGroups;
+  // Accumulators: `ni` issuers x `d_bufs` buffers of `d_cols` columns each in the
+  // 256 TMEM columns after the A ring; buffer d of issuer i starts at column
+  // kDCol0 + (d * ni + i) * d_cols.
+  const uint32_t ni = static_cast<uint32_t>(p.issuers);
+  const uint32_t d_cols = static_cast<uint32_t>(p.mma_n);
+  const uint32_t d_bufs = 2u * ni * d_cols <= 256u ? 2u : 1u;
+  const int32_t k_iters = (p.k + kBlockK - 1) / kBlockK;
+  const bool k_tail_half = (p.k % kBlockK) != 0;  // last stage carries 64 K values only
 
   // ------------------------------------------------------------------ setup --
   if (threadIdx.x == 0) {
     ptx::prefetch_tensormap(&tm_w);
     ptx::prefetch_tensormap(&tm_s);
     ptx::prefetch_tensormap(&tm_x);
-    const uint32_t full_count = p.x_load == kXLoadCpAsync ? 33u : 1u;
-    for (uint32_t s = 0; s < stages; ++s) {
-      ptx::mbar_init(ptx::smem_u32(&sh.full[s]), full_count);
-      ptx::mbar_init(ptx::smem_u32(&sh.empty[s]), 5);
+    for (uint32_t s = 0; s < w_stages; ++s) {
+      ptx::mbar_init(ptx::smem_u32(&sh.wfull[s]), 2);
+      ptx::mbar_init(ptx::smem_u32(&sh.wempty[s]), 4);
+    }
+    // One arrival per gathering warp, or one transaction-count arrival.
+    const uint32_t xfull_count = p.x_load == kXLoadCpAsync ? kHelperThreads / 32 : 1u;
+    for (uint32_t s = 0; s < x_stages; ++s) {
+      ptx::mbar_init(ptx::smem_u32(&sh.xfull[s]), xfull_count);
+      ptx::mbar_init(ptx::smem_u32(&sh.xempty[s]), 1);
     }
     for (uint32_t a = 0; a < kASlots; ++a) {
       ptx::mbar_init(ptx::smem_u32(&sh.afull[a]), 4);
       ptx::mbar_init(ptx::smem_u32(&sh.aempty[a]), 1);
     }
     for (uint32_t d = 0; d < 2; ++d) {
-      ptx::mbar_init(ptx::smem_u32(&sh.dfull[d]), 1);
+      ptx::mbar_init(ptx::smem_u32(&sh.dfull[d]), ni);
       ptx::mbar_init(ptx::smem_u32(&sh.dempty[d]), 4);
     }
     sh.abort_flag = 0;
@@ -344,7 +429,7 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
     ptx::tmem_relinquish();
   }
   // Token slots no load ever fills must not hold NaN patterns.
-  for (uint32_t i = threadIdx.x; i < stages * x_stage_bytes / 16; i += blockDim.x) {
+  for (uint32_t i = threadIdx.x; i < x_stages * x_stage_bytes / 16; i += blockDim.x) {
     reinterpret_cast<uint4*>(smem_x)[i] = make_uint4(0, 0, 0, 0);
   }
   // Number of M tiles.
@@ -382,134 +467,318 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
   iter.init(tiles, k_iters, static_cast<int32_t>(gridDim.x), static_cast<int32_t>(blockIdx.x));
   Segment seg;
 
-  if (warp == 0) {
-    // -------------------------------------------------------------- producer --
-    uint32_t it = 0;
-    bool ok = true;
-    while (ok && iter.next(seg)) {
-      const TileInfo t = decode_tile(p, sh, seg.tile);
-      if (!t.valid) continue;
-      // Token slots loaded per stage: whole groups of four rows.
-      const int32_t load_groups = (t.ntok + 3) >> 2;
-      int32_t rows[2][4];
-#pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        const int32_t gi = static_cast<int32_t>(lane) + 32 * h;
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const int32_t slot = gi * 4 + j;
-          rows[h][j] = (gi < load_groups && slot < t.ntok) ? x_row_of(p, t, slot) : p.x_rows;
+  if (warp == 0 || warp == 1) {
+    // ------------------------- producers: packed weights (warp 0), scales (warp 1) --
+    if (lane == 0) {
+      const bool weights = warp == 0;
+      const CUtensorMap* map = weights ? &tm_w : &tm_s;
+      uint8_t* ring = weights ? smem_w : smem_s;
+      const uint32_t stage_bytes = weights ? kWStageBytes : kSStageBytes;
+      const int32_t rows_per_stage = weights ? kBlockK / 16 : kBlockK / 32;
+      const int32_t rows_per_expert = weights ? p.k / 16 : p.k / 32;
+      StageCursor cur;
+      bool ok = true;
+      CHORD_PROF_INIT();
+      while (ok && iter.next(seg)) {
+        const TileInfo t = decode_tile(p, sh, seg.tile);
+        if (!t.valid) continue;
+        const int32_t col = weights ? 2 * t.n0 : t.n0;
+        int32_t row = t.expert * rows_per_expert + seg.kb * rows_per_stage;
+        for (int32_t kb = seg.kb; kb < seg.ke; ++kb) {
+          CHORD_PROF_T(pt0);
+          if (!ptx::mbar_wait(ptx::smem_u32(&sh.wempty[cur.s]), cur.ph ^ 1u, abort_flag)) {
+            ok = false;
+            break;
+          }
+          CHORD_PROF_ADD(1, pt0);
+          CHORD_PROF_T(pt1);
+          const uint32_t full = ptx::smem_u32(&sh.wfull[cur.s]);
+          ptx::mbar_arrive_expect_tx(full, stage_bytes);
+          ptx::tma_load_2d(ptx::smem_u32(ring + cur.s * stage_bytes), map, full, col, row);
+          row += rows_per_stage;
+          cur.advance(w_stages);
+          CHORD_PROF_ADD(2, pt1);
         }
       }
-      if (p.x_load == kXLoadCpAsync) {
+      if (weights) CHORD_PROF_FLUSH(0); else CHORD_PROF_FLUSH(4);
+      if (!ok) {
+        sh.abort_flag = 1;
+        if (p.status) atomicOr(p.status, kStatusProducerTimeout);
+      }
+    }
+    __syncwarp();
+  } else if (warp < kFirstIssuerWarp) {
+    // ------------------------------------------------ warps 2-3: activations --
+    StageCursor cur;
+    bool ok = true;
+    CHORD_PROF_INIT();
+    if (p.x_load == kXLoadTiled) {
+      // Consecutive rows: one box per 64-wide K half, issued by one thread.
+      while (ok && threadIdx.x == 64 && iter.next(seg)) {
+        const TileInfo t = decode_tile(p, sh, seg.tile);
+        if (!t.valid) continue;
+        int32_t k_col = seg.kb * kBlockK;
+        const int32_t x_row0 = t.base + t.m0;
+        for (int32_t kb = seg.kb; kb < seg.ke; ++kb) {
+          if (!ptx::mbar_wait(ptx::smem_u32(&sh.xempty[cur.s]), cur.ph ^ 1u, abort_flag)) {
+            ok = false;
+            break;
+          }
+          const uint32_t full = ptx::smem_u32(&sh.xfull[cur.s]);
+          const uint32_t xs = ptx::smem_u32(smem_x + cur.s * x_stage_bytes);
+          ptx::mbar_arrive_expect_tx(full, x_stage_bytes);
+          ptx::tma_load_2d(xs, &tm_x, full, k_col, x_row0);
+          ptx::tma_load_2d(xs + x_half_bytes, &tm_x, full, k_col + 64, x_row0);
+          k_col += kBlockK;
+          cur.advance(x_stages);
+        }
+      }
+    } else if (p.x_load == kXLoadGather4) {
+      // Routed rows by TMA: four rows per instruction, lanes of warp 2 own the row
+      // groups lane and lane + 32.
+      while (ok && warp == 2 && iter.next(seg)) {
+        const TileInfo t = decode_tile(p, sh, seg.tile);
+        if (!t.valid) continue;
+        int32_t rows[2][4];
+        const int32_t load_groups = (t.ntok + 3) >> 2;
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
           const int32_t gi = static_cast<int32_t>(lane) + 32 * h;
-          if (gi < load_groups) {
 #pragma unroll
-            for (int j = 0; j < 4; ++j) sh.x_row[gi * 4 + j] = rows[h][j];
+          for (int j = 0; j < 4; ++j) {
+            const int32_t slot = gi * 4 + j;
+            rows[h][j] = (gi < load_groups && slot < t.ntok) ? x_row_of(p, t, slot) : p.x_rows;
           }
         }
-        __syncwarp();
-      }
-      const uint32_t tx_bytes = kWStageBytes + kSStageBytes +
-                                (p.x_load == kXLoadGather4 ? load_groups * 512u : 0u);
-      for (int32_t kb = seg.kb; kb < seg.ke; ++kb, ++it) {
-        const uint32_t s = it % stages;
-        const uint32_t ph = (it / stages) & 1u;
-        if (!ptx::mbar_wait_warp(ptx::smem_u32(&sh.empty[s]), ph ^ 1u, abort_flag)) {
-          ok = false;
-          break;
-        }
-        const uint32_t full = ptx::smem_u32(&sh.full[s]);
-        if (lane == 0) {
-          ptx::mbar_arrive_expect_tx(full, tx_bytes);
-          ptx::tma_load_2d(ptx::smem_u32(smem_w + s * kWStageBytes), &tm_w, full, 2 * t.n0,
-                           t.expert * (p.k / 16) + kb * (kBlockK / 16));
-          ptx::tma_load_2d(ptx::smem_u32(smem_s + s * kSStageBytes), &tm_s, full, t.n0,
-                           t.expert * (p.k / 32) + kb * (kBlockK / 32));
-        }
-        __syncwarp();
-        const uint32_t xs = ptx::smem_u32(smem_x + s * x_stage_bytes);
-        if (p.x_load == kXLoadGather4) {
+        const uint32_t tx_bytes = static_cast<uint32_t>(load_groups) * 1024u;
+        int32_t k_col = seg.kb * kBlockK;
+        for (int32_t kb = seg.kb; kb < seg.ke; ++kb) {
+          if (!ptx::mbar_wait_warp(ptx::smem_u32(&sh.xempty[cur.s]), cur.ph ^ 1u, abort_flag)) {
+            ok = false;
+            break;
+          }
+          const uint32_t full = ptx::smem_u32(&sh.xfull[cur.s]);
+          const uint32_t xs = ptx::smem_u32(smem_x + cur.s * x_stage_bytes);
+          if (lane == 0) ptx::mbar_arrive_expect_tx(full, tx_bytes);
+          __syncwarp();
 #pragma unroll
           for (int h = 0; h < 2; ++h) {
             const int32_t gi = static_cast<int32_t>(lane) + 32 * h;
             if (gi < load_groups) {
-              ptx::tma_gather4(xs + gi * 512u, &tm_x, full, kb * kBlockK, rows[h][0], rows[h][1],
+              ptx::tma_gather4(xs + gi * 512u, &tm_x, full, k_col, rows[h][0], rows[h][1],
                                rows[h][2], rows[h][3]);
+              ptx::tma_gather4(xs + x_half_bytes + gi * 512u, &tm_x, full, k_col + 64, rows[h][0],
+                               rows[h][1], rows[h][2], rows[h][3]);
             }
           }
-        } else {
-          // 8 sixteen-byte chunks per row, XOR-swizzled by (row & 7) like the TMA would.
-          const int32_t chunks = load_groups * 4 * 8;
-          for (int32_t c = lane; c < chunks; c += 32) {
-            const int32_t r = c >> 3, ch = c & 7;
-            const int32_t row = sh.x_row[r];
-            const bool valid = row < p.x_rows;
-            const __nv_bfloat16* src =
-                p.x + static_cast<size_t>(valid ? row : 0) * p.k + kb * kBlockK + ch * 8;
-            ptx::cp_async_16(xs + r * 128u + ((ch ^ (r & 7)) << 4), src, valid);
-          }
-          ptx::cp_async_wait_all();
-          ptx::fence_proxy_async();
-          ptx::mbar_arrive(full);
+          k_col += kBlockK;
+          cur.advance(x_stages);
         }
       }
+    } else {
+      // Routed rows by cp.async: thread = (16-byte chunk of the 256-byte stage row,
+      // row modulo 4).
+      const uint32_t ht = threadIdx.x - 64;
+      const uint32_t ch = ht & 15;
+      const uint32_t half = ch >> 3, ch8 = ch & 7;
+      const uint32_t r0 = ht >> 4;
+      // A stage is published (one arrival per warp: 32 lanes arriving on one mbarrier
+      // would serialise) once its copies have landed, which is checked `depth` stages
+      // later so that the copies of several stages stay in flight.
+      const int32_t depth = x_stages >= 4 ? 2 : 1;
+      StageCursor done;
+      int32_t pending = 0;
+      while (ok && iter.next(seg)) {
+        const TileInfo t = decode_tile(p, sh, seg.tile);
+        if (!t.valid) continue;
+        CHORD_PROF_T(pt9);
+        ptx::named_bar_sync(2, kHelperThreads);  // readers of the previous tile's rows are done
+        // Element offset of each slot's activation row, or -1 for a slot without a token;
+        // x_slots = one past the last slot that carries a token.  Slots beyond it keep
+        // whatever an earlier tile left there: they only feed accumulator columns that
+        // are never stored.
+        if (ht == 0) sh.x_slots = 0;
+        ptx::named_bar_sync(2, kHelperThreads);
+        for (int32_t slot = ht; slot < t.ntok; slot += kHelperThreads) {
+          const int32_t row = x_row_of(p, t, slot);
+          sh.x_row[slot] = row < p.x_rows ? row * p.k : -1;
+          if (row < p.x_rows) atomicMax(&sh.x_slots, slot + 1);
+        }
+        ptx::named_bar_sync(2, kHelperThreads);
+        const int32_t x_slots = sh.x_slots;
+        int32_t k_col = seg.kb * kBlockK + static_cast<int32_t>(ch) * 8;
+        // Decode-sized tiles (at most 16 rows with a token): each thread owns at most
+        // four copies per stage, whose addresses live in registers for the whole tile.
+        const bool few_rows = x_slots <= 16;
+        const __nv_bfloat16* fsrc[4];
+        uint32_t fdst[4];
+        bool fact[4], fval[4];
+#pragma unroll
+        for (int b = 0; b < 4; ++b) {
+          const uint32_t rr = r0 + 4 * b;
+          fact[b] = few_rows && static_cast<int32_t>(rr) < x_slots;
+          const int32_t off = fact[b] ? sh.x_row[rr] : -1;
+          fval[b] = off >= 0;
+          fsrc[b] = p.x + (fval[b] ? off : 0) + k_col;
+          fdst[b] = half * x_half_bytes + rr * 128u + ((ch8 ^ (rr & 7u)) << 4);
+        }
+        CHORD_PROF_ADD(3, pt9);
+        for (int32_t kb = seg.kb; kb < seg.ke; ++kb) {
+          CHORD_PROF_T(pt0);
+          if (!ptx::mbar_wait_warp(ptx::smem_u32(&sh.xempty[cur.s]), cur.ph ^ 1u, abort_flag)) {
+            ok = false;
+            break;
+          }
+          CHORD_PROF_ADD(1, pt0);
+          CHORD_PROF_T(pt1);
+          const uint32_t xs = ptx::smem_u32(smem_x + cur.s * x_stage_bytes);
+          const bool col_ok = k_col + 8 <= p.k;
+          if (few_rows) {
+#pragma unroll
+            for (int b = 0; b < 4; ++b) {
+              if (fact[b] && !CHORD_ABLATE(3)) ptx::cp_async_16(xs + fdst[b], fsrc[b], fval[b] && col_ok);
+              fsrc[b] += kBlockK;
+            }
+          } else {
+            const __nv_bfloat16* xk = p.x + k_col;
+            // Four rows per round: the offset loads go first so that the copies that
+            // follow do not each wait on a shared-memory round trip.
+            for (int32_t r = r0; r < x_slots; r += 16) {
+              int32_t off[4];
+#pragma unroll
+              for (int b = 0; b < 4; ++b) off[b] = (r + 4 * b < x_slots) ? sh.x_row[r + 4 * b] : -1;
+#pragma unroll
+              for (int b = 0; b < 4; ++b) {
+                const uint32_t rr = static_cast<uint32_t>(r + 4 * b);
+                if (static_cast<int32_t>(rr) < x_slots) {
+                  const bool valid = col_ok && off[b] >= 0;
+                  ptx::cp_async_16(xs + half * x_half_bytes + rr * 128u + ((ch8 ^ (rr & 7u)) << 4),
+                                   xk + (valid ? off[b] : 0), valid);
+                }
+              }
+            }
+          }
+          ptx::cp_async_commit();
+          if (++pending > depth) {
+            // The MMA issuer adds the generic-to-async proxy fence after its wait.
+            if (depth == 2) ptx::cp_async_wait_group<2>(); else ptx::cp_async_wait_group<1>();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&sh.xfull[done.s]));
+            done.advance(x_stages);
+            --pending;
+          }
+          k_col += kBlockK;
+          cur.advance(x_stages);
+          CHORD_PROF_ADD(2, pt1);
+        }
+      }
+      if (warp == 2) CHORD_PROF_FLUSH(5);
+      // Drain: publish what is still in flight (also when leaving on a timeout).
+      ptx::cp_async_wait_all();
+      __syncwarp();
+      for (; pending > 0; --pending) {
+        if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&sh.xfull[done.s]));
+        done.advance(x_stages);
+      }
     }
+    __syncwarp();
     if (!ok && lane == 0) {
       sh.abort_flag = 1;
       if (p.status) atomicOr(p.status, kStatusProducerTimeout);
     }
-  } else if (warp == 1) {
-    // ------------------------------------------------------------ MMA issuer --
-    if (lane == 0) {
+  } else if (warp < kFirstDequantWarp) {
+    // ----------------------------------------------------------- MMA issuers --
+    const uint32_t me = warp - kFirstIssuerWarp;
+    if (me < ni && lane == 0) {
       const uint32_t idesc = ptx::idesc_bf16_f32(kBlockN, static_cast<uint32_t>(p.mma_n));
+      const uint64_t xdesc0 = ptx::smem_desc_k_sw128(ptx::smem_u32(smem_x));
+      const uint64_t xdesc_stage = x_stage_bytes >> 4;  // descriptor address units are 16 bytes
+      const uint64_t xdesc_half = x_half_bytes >> 4;
+      uint64_t xdesc = xdesc0;
+      StageCursor cur;
       uint32_t it = 0, segc = 0;
       bool ok = true;
+      CHORD_PROF_INIT();
       while (ok && iter.next(seg)) {
         const TileInfo t = decode_tile(p, sh, seg.tile);
         if (!t.valid) continue;
-        const uint32_t d = segc % d_bufs;
-        const uint32_t dph = (segc / d_bufs) & 1u;
+        const uint32_t d = d_bufs == 2 ? (segc & 1u) : 0u;
+        const uint32_t dph = d_bufs == 2 ? ((segc >> 1) & 1u) : (segc & 1u);
+        CHORD_PROF_T(pt0);
         if (!ptx::mbar_wait(ptx::smem_u32(&sh.dempty[d]), dph ^ 1u, abort_flag)) {
           ok = false;
           break;
         }
+        CHORD_PROF_ADD(1, pt0);
         ptx::tc_fence_after();
-        const uint32_t d_addr = tmem_base + kDCol0 + d * d_stride;
+        const uint32_t d_addr = tmem_base + kDCol0 + (d * ni + me) * d_cols;
+        uint32_t acc = 0;
         for (int32_t kb = seg.kb; kb < seg.ke; ++kb, ++it) {
-          const uint32_t s = it % stages;
-          const uint32_t ph = (it / stages) & 1u;
-          const uint32_t a = it % kASlots;
-          const uint32_t aph = (it / kASlots) & 1u;
-          if (!ptx::mbar_wait(ptx::smem_u32(&sh.full[s]), ph, abort_flag) ||
-              !ptx::mbar_wait(ptx::smem_u32(&sh.afull[a]), aph, abort_flag)) {
-            ok = false;
-            break;
+          if ((it & (ni - 1)) == me) {
+            const uint32_t a = (it & 3u) << 1;  // slot of the first K half; the second is a + 1
+            const uint32_t aph = (it >> 2) & 1u;
+            CHORD_PROF_T(pt1);
+            if (!ptx::mbar_wait(ptx::smem_u32(&sh.xfull[cur.s]), cur.ph, abort_flag)) {
+              ok = false;
+              break;
+            }
+            CHORD_PROF_ADD(2, pt1);
+            if (p.x_load == kXLoadCpAsync) ptx::fence_proxy_async();
+            CHORD_PROF_T(pt2);
+            if (!ptx::mbar_wait(ptx::smem_u32(&sh.afull[a]), aph, abort_flag)) {
+              ok = false;
+              break;
+            }
+            CHORD_PROF_ADD(3, pt2);
+            CHORD_PROF_T(pt3);
+            ptx::tc_fence_after();
+            const uint32_t a_addr = tmem_base + a * kAColsPerSlot;
+            if (!CHORD_ABLATE(0)) {
+              ptx::mma_ts(d_addr, a_addr, xdesc, idesc, acc);
+              ptx::mma_ts(d_addr, a_addr + 8, xdesc + 2, idesc, 1);
+              ptx::mma_ts(d_addr, a_addr + 16, xdesc + 4, idesc, 1);
+              ptx::mma_ts(d_addr, a_addr + 24, xdesc + 6, idesc, 1);
+            }
+            ptx::mma_commit(ptx::smem_u32(&sh.aempty[a]));
+            CHORD_PROF_ADD(4, pt3);
+            CHORD_PROF_T(pt4);
+            if (!ptx::mbar_wait(ptx::smem_u32(&sh.afull[a + 1]), aph, abort_flag)) {
+              ok = false;
+              break;
+            }
+            CHORD_PROF_ADD(3, pt4);
+            CHORD_PROF_T(pt5);
+            ptx::tc_fence_after();
+            if (!(k_tail_half && kb == k_iters - 1) && !CHORD_ABLATE(0)) {
+              const uint64_t xd1 = xdesc + xdesc_half;
+              ptx::mma_ts(d_addr, a_addr + 32, xd1, idesc, 1);
+              ptx::mma_ts(d_addr, a_addr + 40, xd1 + 2, idesc, 1);
+              ptx::mma_ts(d_addr, a_addr + 48, xd1 + 4, idesc, 1);
+              ptx::mma_ts(d_addr, a_addr + 56, xd1 + 6, idesc, 1);
+            }
+            acc = 1;
+            ptx::mma_commit(ptx::smem_u32(&sh.aempty[a + 1]));
+            ptx::mma_commit(ptx::smem_u32(&sh.xempty[cur.s]));
+            CHORD_PROF_ADD(4, pt5);
           }
-          ptx::tc_fence_after();
-          const uint32_t a_addr = tmem_base + a * kAColsPerSlot;
-          const uint32_t xs = ptx::smem_u32(smem_x + s * x_stage_bytes);
-#pragma unroll
-          for (int j = 0; j < kBlockK / 16; ++j) {
-            ptx::mma_ts(d_addr, a_addr + 8 * j, ptx::smem_desc_k_sw128(xs + 32 * j), idesc,
-                        (kb > seg.kb || j > 0) ? 1u : 0u);
-          }
-          ptx::mma_commit(ptx::smem_u32(&sh.empty[s]));
-          ptx::mma_commit(ptx::smem_u32(&sh.aempty[a]));
+          xdesc += xdesc_stage;
+          cur.advance(x_stages);
+          if (cur.s == 0) xdesc = xdesc0;
         }
         if (!ok) break;
-        ptx::mma_commit(ptx::smem_u32(&sh.dfull[d]));
+        // One arrival per issuer and segment, also from an issuer that had no stage in it.
+        if (acc != 0) ptx::mma_commit(ptx::smem_u32(&sh.dfull[d]));
+        else ptx::mbar_arrive(ptx::smem_u32(&sh.dfull[d]));
         ++segc;
       }
+      if (me == 0) CHORD_PROF_FLUSH(1);
       if (!ok) {
         sh.abort_flag = 1;
         if (p.status) atomicOr(p.status, kStatusMmaTimeout);
       }
     }
     __syncwarp();
-  } else if (warp >= kFirstDequantWarp && warp < kFirstEpilogueWarp) {
+  } else if (warp < kFirstEpilogueWarp) {
     // --------------------------------------------------------------- dequant --
     const uint32_t group = (warp - kFirstDequantWarp) >> 2;
     const uint32_t q = warp & 3;  // TMEM lane quarter == 32 weight rows
@@ -517,89 +786,115 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
     // 64-row chunk q>>1) inside one K16 row of the stage, and of its four scales.
     const uint32_t w_off = (q >> 1) * 512u + lane * 16u + (q & 1) * 8u;
     const uint32_t s_off = (q >> 1) * 128u + (lane >> 2) * 16u + (q & 1) * 8u;
+    StageCursor cur;
     uint32_t it = 0;
     bool ok = true;
+    CHORD_PROF_INIT();
     while (ok && iter.next(seg)) {
       const TileInfo t = decode_tile(p, sh, seg.tile);
       if (!t.valid) continue;
-      for (int32_t kb = seg.kb; kb < seg.ke; ++kb, ++it) {
-        if (it % kDequantGroups != group) continue;
-        const uint32_t s = it % stages;
-        const uint32_t ph = (it / stages) & 1u;
-        const uint32_t a = it % kASlots;
-        const uint32_t aph = (it / kASlots) & 1u;
-        if (!ptx::mbar_wait_warp(ptx::smem_u32(&sh.full[s]), ph, abort_flag)) {
+      for (int32_t kb = seg.kb; kb < seg.ke; ++kb, ++it, cur.advance(w_stages)) {
+        if ((it & (kDequantGroups - 1)) != group) continue;
+        const uint32_t a = (it & 3u) << 1;  // slots a (first K half) and a + 1 (second)
+        const uint32_t aph = (it >> 2) & 1u;
+        CHORD_PROF_T(pt0);
+        if (!ptx::mbar_wait_warp(ptx::smem_u32(&sh.wfull[cur.s]), cur.ph, abort_flag)) {
           ok = false;
           break;
         }
-        uint2 words[kBlockK / 16];
-        uint2 scales[kBlockK / 32];
-        const uint8_t* wsrc = smem_w + s * kWStageBytes + w_off;
-        const uint8_t* ssrc = smem_s + s * kSStageBytes + s_off;
-#pragma unroll
-        for (int j = 0; j < kBlockK / 16; ++j) {
-          words[j] = *reinterpret_cast<const uint2*>(wsrc + j * 1024);
-        }
-#pragma unroll
-        for (int g = 0; g < kBlockK / 32; ++g) {
-          scales[g] = *reinterpret_cast<const uint2*>(ssrc + g * 256);
-        }
-        __syncwarp();
-        if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&sh.empty[s]));
-
-        uint32_t lo[16], hi[16];  // lanes 0-15 (first slab) and 16-31 (second slab) of the quarter
-#pragma unroll
-        for (int j = 0; j < kBlockK / 16; ++j) {
-          const uint2 sc = scales[j >> 1];
-          // sc.x = {slab A row r, slab A row r+8}; sc.y = same for slab B.
-          const uint32_t a_lo = __byte_perm(sc.x, 0, 0x1010);
-          const uint32_t a_hi = __byte_perm(sc.x, 0, 0x3232);
-          const uint32_t b_lo = __byte_perm(sc.y, 0, 0x1010);
-          const uint32_t b_hi = __byte_perm(sc.y, 0, 0x3232);
-          dequant_word(words[j].x, a_lo, a_hi, lo + 4 * j);
-          dequant_word(words[j].y, b_lo, b_hi, hi + 4 * j);
-        }
-        if (!ptx::mbar_wait_warp(ptx::smem_u32(&sh.aempty[a]), aph ^ 1u, abort_flag)) {
-          ok = false;
-          break;
-        }
-        ptx::tc_fence_after();
+        CHORD_PROF_ADD(1, pt0);
+        const uint8_t* wsrc = smem_w + cur.s * kWStageBytes + w_off;
+        const uint8_t* ssrc = smem_s + cur.s * kSStageBytes + s_off;
         const uint32_t a_addr = tmem_base + ((q * 32u) << 16) + a * kAColsPerSlot;
-        ptx::tmem_st_16x128b_x8(a_addr, lo);
-        ptx::tmem_st_16x128b_x8(a_addr + (16u << 16), hi);
-        ptx::tmem_wait_st();
-        ptx::tc_fence_before();
-        __syncwarp();
-        if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&sh.afull[a]));
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {  // two 64-wide K halves
+          CHORD_PROF_T(pt1);
+          uint2 words[4];
+          uint2 scales[2];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            words[j] = *reinterpret_cast<const uint2*>(wsrc + (4 * h + j) * 1024);
+          }
+#pragma unroll
+          for (int g = 0; g < 2; ++g) {
+            scales[g] = *reinterpret_cast<const uint2*>(ssrc + (2 * h + g) * 256);
+          }
+          if (h == 1) {
+            // Last read of this stage's shared memory: hand it back to the producer.
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&sh.wempty[cur.s]));
+          }
+          uint32_t lo[16], hi[16];  // TMEM lanes 0-15 (first slab) and 16-31 (second slab)
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const uint2 sc = scales[j >> 1];
+            // sc.x = {slab A row r, slab A row r+8}; sc.y = same for slab B.
+            const uint32_t a_lo = __byte_perm(sc.x, 0, 0x1010);
+            const uint32_t a_hi = __byte_perm(sc.x, 0, 0x3232);
+            const uint32_t b_lo = __byte_perm(sc.y, 0, 0x1010);
+            const uint32_t b_hi = __byte_perm(sc.y, 0, 0x3232);
+            if (CHORD_ABLATE(1)) {
+#pragma unroll
+              for (int z = 0; z < 4; ++z) {
+                lo[4 * j + z] = words[j].x ^ a_lo;
+                hi[4 * j + z] = words[j].y ^ b_hi;
+              }
+            } else {
+              dequant_word(words[j].x, a_lo, a_hi, lo + 4 * j);
+              dequant_word(words[j].y, b_lo, b_hi, hi + 4 * j);
+            }
+          }
+          CHORD_PROF_ADD(2, pt1);
+          CHORD_PROF_T(pt2);
+          if (!ptx::mbar_wait_warp(ptx::smem_u32(&sh.aempty[a + h]), aph ^ 1u, abort_flag)) {
+            ok = false;
+            break;
+          }
+          CHORD_PROF_ADD(3, pt2);
+          CHORD_PROF_T(pt3);
+          ptx::tc_fence_after();
+          if (!CHORD_ABLATE(2)) {
+            ptx::tmem_st_16x128b_x8(a_addr + 32 * h, lo);
+            ptx::tmem_st_16x128b_x8(a_addr + (16u << 16) + 32 * h, hi);
+          } else if (lo[3] == 0x12345678u && hi[5] == 0x9abcdef0u) {
+            sh.x_slots = 1;  // keeps the dequantised values alive
+          }
+          ptx::tmem_wait_st();
+          ptx::tc_fence_before();
+          __syncwarp();
+          if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&sh.afull[a + h]));
+          CHORD_PROF_ADD(4, pt3);
+        }
+        if (!ok) break;
       }
     }
+    if (warp == kFirstDequantWarp) CHORD_PROF_FLUSH(2);
     if (!ok && lane == 0) {
       sh.abort_flag = 1;
       if (p.status) atomicOr(p.status, kStatusDequantTimeout);
     }
-  } else if (warp >= kFirstEpilogueWarp) {
+  } else {
     // -------------------------------------------------------------- epilogue --
     const uint32_t q = warp & 3;
     const uint32_t et = threadIdx.x - kFirstEpilogueWarp * 32;  // 0..127 == TMEM lane
-    const uint32_t row_in_tile = q * 32 + lane;                 // == et
-    uint32_t segc = 0;
+    uint32_t segc = 0, it0 = 0;
     bool ok = true;
+    CHORD_PROF_INIT();
     const size_t ws_slot = static_cast<size_t>(kBlockN) * p.mma_n;
     while (ok && iter.next(seg)) {
       const TileInfo t = decode_tile(p, sh, seg.tile);
       if (!t.valid) continue;
-      const uint32_t d = segc % d_bufs;
-      const uint32_t dph = (segc / d_bufs) & 1u;
+      const uint32_t d = d_bufs == 2 ? (segc & 1u) : 0u;
+      const uint32_t dph = d_bufs == 2 ? ((segc >> 1) & 1u) : (segc & 1u);
       ptx::named_bar_sync(1, 128);  // previous segment's out_row readers are done
       for (int32_t c = et; c < p.mma_n; c += 128) sh.out_row[c] = out_row_of(p, t, c);
-      int32_t lock_ok = 1;
       if (seg.type == kSegOwner && et == 0) {
         // Wait (bounded) until every other slice of this tile has published its partial.
         const int* lock = p.locks + blockIdx.x;
-        lock_ok = 0;
+        bool lock_ok = false;
         for (uint32_t spin = 0; spin < (1u << 22); ++spin) {
           if (ptx::ld_acquire(lock) >= seg.peer) {
-            lock_ok = 1;
+            lock_ok = true;
             break;
           }
           __nanosleep(64);
@@ -608,6 +903,7 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
       }
       // The four warps must agree on the outcome before any of them leaves the loop,
       // or the named barriers below would wait for warps that are gone.
+      CHORD_PROF_T(pt0);
       if (!ptx::mbar_wait_warp(ptx::smem_u32(&sh.dfull[d]), dph, abort_flag) && lane == 0) {
         sh.epilogue_failed = 1;
       }
@@ -617,21 +913,31 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
         ok = false;
         break;
       }
-      const uint32_t d_addr = tmem_base + ((q * 32u) << 16) + kDCol0 + d * d_stride;
-      __nv_bfloat16* out_col = p.out + t.n0 + row_in_tile;
+      CHORD_PROF_ADD(1, pt0);
+      CHORD_PROF_T(pt1);
+      const uint32_t d_addr = tmem_base + ((q * 32u) << 16) + kDCol0 + d * ni * d_cols;
+      __nv_bfloat16* out_col = p.out + t.n0 + et;
+      // Issuer i accumulated the stages it0 + j with (it0 + j) % ni == i; it took part
+      // in this segment only if one of them falls inside it.
+      const uint32_t seg_len = static_cast<uint32_t>(seg.ke - seg.kb);
       for (int32_t c0 = 0; c0 < p.mma_n; c0 += 16) {
-        uint32_t v[16];
-        ptx::tmem_ld_32x32b_x16(d_addr + c0, v);
-        ptx::tmem_wait_ld();
+        float acc[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) acc[j] = 0.0f;
+        for (uint32_t i = 0; i < ni; ++i) {
+          if (((i - it0) & (ni - 1)) >= seg_len) continue;
+          uint32_t v[16];
+          ptx::tmem_ld_32x32b_x16(d_addr + i * d_cols + c0, v);
+          ptx::tmem_wait_ld();
+#pragma unroll
+          for (int j = 0; j < 16; ++j) acc[j] += __uint_as_float(v[j]);
+        }
         if (seg.type == kSegContrib) {
           float* dst = p.workspace + blockIdx.x * ws_slot + static_cast<size_t>(c0) * kBlockN + et;
 #pragma unroll
-          for (int j = 0; j < 16; ++j) __stcg(dst + j * kBlockN, __uint_as_float(v[j]));
+          for (int j = 0; j < 16; ++j) __stcg(dst + j * kBlockN, acc[j]);
           continue;
         }
-        float acc[16];
-#pragma unroll
-        for (int j = 0; j < 16; ++j) acc[j] = __uint_as_float(v[j]);
         if (seg.type == kSegOwner) {
           for (int32_t peer = 1; peer <= seg.peer; ++peer) {
             const float* src = p.workspace + (blockIdx.x + peer) * ws_slot +
@@ -658,8 +964,11 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
         ptx::named_bar_sync(1, 128);
         if (et == 0) p.locks[blockIdx.x] = 0;
       }
+      CHORD_PROF_ADD(2, pt1);
       ++segc;
+      it0 += seg_len;
     }
+    if (warp == kFirstEpilogueWarp) CHORD_PROF_FLUSH(3);
     if (!ok && lane == 0) {
       sh.abort_flag = 1;
       if (p.status) atomicOr(p.status, kStatusEpilogueTimeout);

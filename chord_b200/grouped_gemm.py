@@ -9,7 +9,7 @@ from __future__ import annotations
 import torch
 
 from . import _lib
-from .indexed import gemm_scratch, status_word
+from .indexed_gemm import gemm_scratch, status_word
 from .packing import PreparedWeight, _validate_supported_architecture
 
 

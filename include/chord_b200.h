@@ -40,7 +40,8 @@ const char* chord_b200_last_error(void);
 /* Library build tag, e.g. "chord_b200 sm_100a". */
 const char* chord_b200_version(void);
 
-/* Tuning knobs for sweeps: "x_load" (0 TMA gather4, 1 cp.async),
+/* Tuning knobs for sweeps: "x_load" (routed-row gather of `indexed`: 0 cp.async
+ * helper warps, 1 TMA tile::gather4),
  * "dequant_groups" (2 or 4), "max_stages" (0 = auto), "grid_limit" (0 = one
  * CTA per SM).  Counterpart of the reference's CHORD_W4A16_* environment
  * overrides (chord_kernels/operator/grouped/heuristics.py:32-39).  Process-wide. */
