@@ -588,7 +588,7 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
       const int32_t depth = x_stages >= 4 ? 2 : 1;
       StageCursor done;
       int32_t pending = 0;
-      while (ok && iter.next(seg)) {
+      while (ok && !CHORD_ABLATE(4) && iter.next(seg)) {
         const TileInfo t = decode_tile(p, sh, seg.tile);
         if (!t.valid) continue;
         CHORD_PROF_T(pt9);
@@ -718,7 +718,8 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
             const uint32_t a = (it & 3u) << 1;  // slot of the first K half; the second is a + 1
             const uint32_t aph = (it >> 2) & 1u;
             CHORD_PROF_T(pt1);
-            if (!ptx::mbar_wait(ptx::smem_u32(&sh.xfull[cur.s]), cur.ph, abort_flag)) {
+            if (!CHORD_ABLATE(4) &&
+                !ptx::mbar_wait(ptx::smem_u32(&sh.xfull[cur.s]), cur.ph, abort_flag)) {
               ok = false;
               break;
             }
@@ -789,6 +790,69 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
     StageCursor cur;
     uint32_t it = 0;
     bool ok = true;
+    // A stored K half is published to the MMA issuer one compute step later (after
+    // the next half has been dequantised), so that the latency of the tensor-memory
+    // store and of the barrier round trip hides behind ALU work.  `pending` is the
+    // slot whose store has been issued but not yet published.
+    int32_t pending = -1;
+    auto publish = [&]() {
+      if (pending >= 0) {
+        ptx::tmem_wait_st();
+        ptx::tc_fence_before();
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&sh.afull[pending]));
+        pending = -1;
+      }
+    };
+    auto load_half = [&](const uint8_t* wsrc, const uint8_t* ssrc, int h, uint2 (&words)[4],
+                         uint2 (&scales)[2]) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        words[j] = *reinterpret_cast<const uint2*>(wsrc + (4 * h + j) * 1024);
+      }
+#pragma unroll
+      for (int g = 0; g < 2; ++g) {
+        scales[g] = *reinterpret_cast<const uint2*>(ssrc + (2 * h + g) * 256);
+      }
+    };
+    auto dequant_half = [&](const uint2 (&words)[4], const uint2 (&scales)[2], uint32_t (&lo)[16],
+                            uint32_t (&hi)[16]) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const uint2 sc = scales[j >> 1];
+        // sc.x = {slab A row r, slab A row r+8}; sc.y = same for slab B.
+        const uint32_t a_lo = __byte_perm(sc.x, 0, 0x1010);
+        const uint32_t a_hi = __byte_perm(sc.x, 0, 0x3232);
+        const uint32_t b_lo = __byte_perm(sc.y, 0, 0x1010);
+        const uint32_t b_hi = __byte_perm(sc.y, 0, 0x3232);
+        if (CHORD_ABLATE(1)) {
+#pragma unroll
+          for (int z = 0; z < 4; ++z) {
+            lo[4 * j + z] = words[j].x ^ a_lo;
+            hi[4 * j + z] = words[j].y ^ b_hi;
+          }
+        } else {
+          dequant_word(words[j].x, a_lo, a_hi, lo + 4 * j);
+          dequant_word(words[j].y, b_lo, b_hi, hi + 4 * j);
+        }
+      }
+    };
+    // Waits for the slot to be free, then stores one K half: lo to TMEM lanes 0-15 of
+    // the quarter (first slab), hi to lanes 16-31 (second slab).
+    auto store_half = [&](uint32_t slot, uint32_t aph, const uint32_t (&lo)[16],
+                          const uint32_t (&hi)[16]) -> bool {
+      if (!ptx::mbar_wait_warp(ptx::smem_u32(&sh.aempty[slot]), aph ^ 1u, abort_flag)) return false;
+      ptx::tc_fence_after();
+      const uint32_t a_addr = tmem_base + ((q * 32u) << 16) + slot * kAColsPerSlot;
+      if (!CHORD_ABLATE(2)) {
+        ptx::tmem_st_16x128b_x8(a_addr, lo);
+        ptx::tmem_st_16x128b_x8(a_addr + (16u << 16), hi);
+      } else if (lo[3] == 0x12345678u && hi[5] == 0x9abcdef0u) {
+        sh.x_slots = 1;  // keeps the dequantised values alive
+      }
+      pending = static_cast<int32_t>(slot);
+      return true;
+    };
     CHORD_PROF_INIT();
     while (ok && iter.next(seg)) {
       const TileInfo t = decode_tile(p, sh, seg.tile);
@@ -805,69 +869,37 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
         CHORD_PROF_ADD(1, pt0);
         const uint8_t* wsrc = smem_w + cur.s * kWStageBytes + w_off;
         const uint8_t* ssrc = smem_s + cur.s * kSStageBytes + s_off;
-        const uint32_t a_addr = tmem_base + ((q * 32u) << 16) + a * kAColsPerSlot;
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {  // two 64-wide K halves
-          CHORD_PROF_T(pt1);
-          uint2 words[4];
-          uint2 scales[2];
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            words[j] = *reinterpret_cast<const uint2*>(wsrc + (4 * h + j) * 1024);
-          }
-#pragma unroll
-          for (int g = 0; g < 2; ++g) {
-            scales[g] = *reinterpret_cast<const uint2*>(ssrc + (2 * h + g) * 256);
-          }
-          if (h == 1) {
-            // Last read of this stage's shared memory: hand it back to the producer.
-            __syncwarp();
-            if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&sh.wempty[cur.s]));
-          }
-          uint32_t lo[16], hi[16];  // TMEM lanes 0-15 (first slab) and 16-31 (second slab)
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const uint2 sc = scales[j >> 1];
-            // sc.x = {slab A row r, slab A row r+8}; sc.y = same for slab B.
-            const uint32_t a_lo = __byte_perm(sc.x, 0, 0x1010);
-            const uint32_t a_hi = __byte_perm(sc.x, 0, 0x3232);
-            const uint32_t b_lo = __byte_perm(sc.y, 0, 0x1010);
-            const uint32_t b_hi = __byte_perm(sc.y, 0, 0x3232);
-            if (CHORD_ABLATE(1)) {
-#pragma unroll
-              for (int z = 0; z < 4; ++z) {
-                lo[4 * j + z] = words[j].x ^ a_lo;
-                hi[4 * j + z] = words[j].y ^ b_hi;
-              }
-            } else {
-              dequant_word(words[j].x, a_lo, a_hi, lo + 4 * j);
-              dequant_word(words[j].y, b_lo, b_hi, hi + 4 * j);
-            }
-          }
-          CHORD_PROF_ADD(2, pt1);
-          CHORD_PROF_T(pt2);
-          if (!ptx::mbar_wait_warp(ptx::smem_u32(&sh.aempty[a + h]), aph ^ 1u, abort_flag)) {
-            ok = false;
-            break;
-          }
-          CHORD_PROF_ADD(3, pt2);
-          CHORD_PROF_T(pt3);
-          ptx::tc_fence_after();
-          if (!CHORD_ABLATE(2)) {
-            ptx::tmem_st_16x128b_x8(a_addr + 32 * h, lo);
-            ptx::tmem_st_16x128b_x8(a_addr + (16u << 16) + 32 * h, hi);
-          } else if (lo[3] == 0x12345678u && hi[5] == 0x9abcdef0u) {
-            sh.x_slots = 1;  // keeps the dequantised values alive
-          }
-          ptx::tmem_wait_st();
-          ptx::tc_fence_before();
-          __syncwarp();
-          if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&sh.afull[a + h]));
-          CHORD_PROF_ADD(4, pt3);
+        uint2 words[4], scales[2];
+        uint32_t lo[16], hi[16];
+        CHORD_PROF_T(pt1);
+        load_half(wsrc, ssrc, 0, words, scales);
+        dequant_half(words, scales, lo, hi);
+        // Second half's words are fetched before the first half is stored, and the
+        // stage goes back to the producers as soon as they are in registers.
+        load_half(wsrc, ssrc, 1, words, scales);
+        CHORD_PROF_ADD(2, pt1);
+        CHORD_PROF_T(pt2);
+        publish();  // previous stage's second half
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&sh.wempty[cur.s]));
+        if (!store_half(a, aph, lo, hi)) {
+          ok = false;
+          break;
         }
-        if (!ok) break;
+        CHORD_PROF_ADD(3, pt2);
+        CHORD_PROF_T(pt3);
+        dequant_half(words, scales, lo, hi);
+        CHORD_PROF_ADD(2, pt3);
+        CHORD_PROF_T(pt4);
+        publish();  // this stage's first half
+        if (!store_half(a + 1, aph, lo, hi)) {
+          ok = false;
+          break;
+        }
+        CHORD_PROF_ADD(4, pt4);
       }
     }
+    publish();
     if (warp == kFirstDequantWarp) CHORD_PROF_FLUSH(2);
     if (!ok && lane == 0) {
       sh.abort_flag = 1;
