@@ -31,6 +31,7 @@ SIGNATURES = {
     "chord_b200_masked_tile_m": (_int, [_i64]),
     "chord_b200_gemm_workspace_bytes": (_i64, [_i64]),
     "chord_b200_gemm_lock_words": (_int, []),
+    "chord_b200_schedule_segments": (_i64, [_i64, _i64, _i64, _i64, _ptr, _i64]),
     "chord_b200_indexed": (_int, [_ptr, _ptr, _ptr, _ptr, _i64, _ptr, _i64, _ptr, _ptr, _ptr, _i64,
                                   _ptr, _i64, _ptr, _i64, _i64, _i64, _i64, _i64, _i64, _ptr]),
     "chord_b200_contiguous": (_int, [_ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _i64, _ptr, _i64, _ptr,

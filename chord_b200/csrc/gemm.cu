@@ -267,6 +267,32 @@ int chord_b200_gemm_lock_words(void) {
   return chord::grid_size(dev);
 }
 
+int64_t chord_b200_schedule_segments(int64_t tiles, int64_t k, int64_t grid, int64_t cta,
+                                     int32_t* out, int64_t capacity) {
+  if (tiles < 0 || k <= 0 || k % 64 || grid <= 0 || cta < 0 || cta >= grid ||
+      tiles > (1ll << 30)) {
+    chord::fail(chord::kInvalidArgument, "bad schedule query");
+    return -1;
+  }
+  chord::SegmentIterator it;
+  it.init(static_cast<int32_t>(tiles), static_cast<int32_t>((k + chord::kBlockK - 1) / chord::kBlockK),
+          static_cast<int32_t>(grid), static_cast<int32_t>(cta));
+  chord::Segment seg;
+  int64_t count = 0;
+  while (it.next(seg)) {
+    if (out != nullptr && count < capacity) {
+      int32_t* rec = out + count * 5;
+      rec[0] = seg.tile;
+      rec[1] = seg.kb;
+      rec[2] = seg.ke;
+      rec[3] = seg.type;
+      rec[4] = seg.peer;
+    }
+    ++count;
+  }
+  return count;
+}
+
 int chord_b200_indexed(const void* x, const int32_t* packed, const void* scale,
                        const int32_t* sorted_ids, int64_t sorted_len, const int32_t* expert_ids,
                        int64_t expert_len, const int32_t* num_tokens_padded, void* out,

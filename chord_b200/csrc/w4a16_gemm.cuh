@@ -181,7 +181,7 @@ struct SegmentIterator {
   int64_t units, u0, u1;
   int32_t geff;
 
-  __device__ void init(int32_t tiles, int32_t k_iters, int32_t grid_, int32_t cta_) {
+  __host__ __device__ void init(int32_t tiles, int32_t k_iters, int32_t grid_, int32_t cta_) {
     grid = grid_;
     cta = cta_;
     ki = k_iters;
@@ -204,11 +204,11 @@ struct SegmentIterator {
     }
   }
 
-  __device__ int32_t cta_of_unit(int64_t u) const {
+  __host__ __device__ int32_t cta_of_unit(int64_t u) const {
     return static_cast<int32_t>(((u + 1) * geff - 1) / units);
   }
 
-  __device__ bool next(Segment& s) {
+  __host__ __device__ bool next(Segment& s) {
     if (wave < dp_waves) {
       s.tile = wave * grid + cta;
       s.kb = 0;

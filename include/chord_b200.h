@@ -82,6 +82,16 @@ int64_t chord_b200_gemm_workspace_bytes(int64_t tile_tokens);
  * The reference needs grid + grid/10 (launcher.cpp:95-109). */
 int chord_b200_gemm_lock_words(void);
 
+/* Host-side view of the tile schedule (no GPU needed): the segments CTA `cta` of a
+ * `grid`-CTA launch works through for `tiles` output tiles of depth `k`.  Writes up
+ * to `capacity` records of five int32 {tile, first k-block, end k-block, type
+ * (0 whole tile, 1 stream-K owner, 2 stream-K contributor), peer (owner: number of
+ * contributors; contributor: owner CTA)} and returns the number of segments, or
+ * < 0 on a bad query.  Counterpart of the reference's Scheduler
+ * (include/humming/scheduler.cuh:73-173), exposed so the split can be checked. */
+int64_t chord_b200_schedule_segments(int64_t tiles, int64_t k, int64_t grid, int64_t cta,
+                                     int32_t* out, int64_t capacity);
+
 /* ---- indexed GEMM: replaces launch_kernel (launcher.cpp:52-158) -------------
  * out[id, :] = x[id / top_k, :] . dequant(W[expert_ids[block of id]])^T for every
  * id < m * top_k found in sorted_ids[0 .. *num_tokens_padded).

@@ -1,0 +1,81 @@
+"""SiLU*mul, routing alignment and the single-GPU expert-parallel layer on the GPU."""
+
+import pytest
+import torch
+
+from oracle import w4a16_oracle as O
+from tests.cases import make_weights
+
+pytestmark = pytest.mark.gpu
+
+
+def test_silu_mul_matches_oracle(device):
+    import chord_b200
+
+    g = torch.Generator().manual_seed(5)
+    gate_up = (torch.randn((37, 4096), generator=g) * 3).to(torch.bfloat16)
+    got = chord_b200.silu_mul(gate_up.to(device)).cpu()
+    want = O.silu_mul(gate_up)
+    # fast exponential on the device: allow one BF16 ulp
+    assert (got.float() - want.float()).abs().max() <= 2.0 ** -7 * want.float().abs().max()
+    assert (got.view(torch.int16) != want.view(torch.int16)).float().mean() < 0.02
+
+
+def test_silu_mul_routed_touches_only_routed_rows(device):
+    import chord_b200
+
+    g = torch.Generator().manual_seed(6)
+    gate_up = torch.randn((64, 512), generator=g).to(torch.bfloat16)
+    topk = O.topk_ids_random(8, 8, 384, g)
+    sorted_ids, _, padded = O.align_routing_blocks(topk, 16, 48, 0)
+    out = torch.full((64, 256), float("nan"), dtype=torch.bfloat16, device=device)
+    if sorted_ids.numel() == 0:
+        pytest.skip("draw routed nothing locally")
+    chord_b200.silu_mul(gate_up.to(device), sorted_ids=sorted_ids.to(device),
+                        num_tokens_padded=padded.to(device).reshape(1), outputs=out)
+    got = out.float().cpu()
+    rows = sorted_ids[sorted_ids < 64].long()
+    mask = torch.zeros(64, dtype=torch.bool)
+    mask[rows] = True
+    assert torch.equal(~torch.isnan(got).any(dim=1), mask)
+    want = O.silu_mul(gate_up).float()
+    assert (got[mask] - want[mask]).abs().max() <= 2.0 ** -7 * want.abs().max()
+
+
+@pytest.mark.parametrize("tokens,top_k,total,local,base,block_m", [
+    (64, 2, 8, 8, 0, 16), (256, 8, 384, 48, 96, 16), (4096, 8, 384, 384, 0, 64), (3, 8, 384, 48, 0, 8),
+    (1, 8, 384, 48, 336, 16), (1000, 4, 64, 64, 0, 128), (0, 8, 384, 48, 0, 16),
+])
+def test_moe_align_block_size_bit_exact(device, tokens, top_k, total, local, base, block_m):
+    import chord_b200
+
+    g = torch.Generator().manual_seed(tokens + block_m)
+    topk = O.topk_ids_random(tokens, top_k, total, g) if tokens else torch.zeros((0, top_k), dtype=torch.int32)
+    s, e, p = chord_b200.moe_align_block_size(topk.to(device), block_m, local, expert_base=base)
+    rs, re, rp = O.align_routing_blocks(topk, block_m, local, base)
+    count = int(p.item())
+    assert count == int(rp)
+    assert torch.equal(s.cpu()[:count], rs)
+    assert torch.equal(e.cpu()[: count // block_m], re)
+
+
+def test_single_gpu_layer_matches_oracle(device):
+    """The expert-parallel layer with one rank: alignment, gate_up, SiLU*mul, down."""
+    import chord_b200
+    from chord_b200 import ep
+
+    experts, hidden, inter, tokens, top_k = 8, 512, 256, 40, 4
+    codes13, scale13 = make_weights(experts, 2 * inter, hidden, 1)
+    codes2, scale2 = make_weights(experts, hidden, inter, 2)
+    g = torch.Generator().manual_seed(7)
+    x = torch.randn((tokens, hidden), generator=g).to(torch.bfloat16)
+    topk = O.topk_ids_random(tokens, top_k, experts, g)
+    w13 = chord_b200.pack_w4a16(codes13.to(device), scale13.to(device))
+    w2 = chord_b200.pack_w4a16(codes2.to(device), scale2.to(device))
+    out = ep.moe_layer(x.to(device), topk.to(device), experts, ep.local_expert_mlp(w13, w2))
+    assert out.shape == (tokens, top_k, hidden)
+    gate_up = O.reference_indexed(x, codes13, scale13, topk, top_k).to(torch.bfloat16)
+    ref = O.reference_indexed(O.silu_mul(gate_up), codes2, scale2, topk, top_k, projection="down")
+    got = out.float().cpu().view(tokens * top_k, hidden)
+    assert O.cosine_diff(got, ref) <= 5e-3
+    assert O.max_abs_rel(got, ref) <= 2e-2      # two GEMMs and an activation in BF16

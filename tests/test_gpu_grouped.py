@@ -1,0 +1,142 @@
+"""`masked` and `contiguous` on the GPU against the CPU oracle, plus the point of
+packing once: one PreparedWeight serves all three operators
+(reference: tests/test_w4a16_grouped.py:407-623; its limit is cos-diff < 1e-3)."""
+
+import pytest
+import torch
+
+from oracle import w4a16_oracle as O
+from tests.cases import make_contiguous_case, make_indexed_case, make_masked_case
+
+pytestmark = pytest.mark.gpu
+
+COS_LIMIT = 1e-3
+REL_LIMIT = 1e-2
+
+
+def _status_ok(device):
+    from chord_b200.indexed_gemm import status_word
+
+    torch.cuda.synchronize()
+    assert int(status_word(device).item()) == 0
+
+
+def _compare(got, ref):
+    got = got.float().cpu()
+    written = ~torch.isnan(got).any(dim=1)
+    expected = ~torch.isnan(ref).any(dim=1)
+    assert torch.equal(written, expected)
+    if expected.any():
+        assert O.cosine_diff(got[expected], ref[expected]) < COS_LIMIT
+        assert O.max_abs_rel(got[expected], ref[expected]) <= REL_LIMIT
+
+
+@pytest.mark.parametrize("groups,max_m,n,k,expected_m", [
+    (6, 40, 512, 256, 8), (12, 256, 1024, 512, 32), (4, 256, 512, 1024, 128),
+    (3, 8, 256, 128, 8), (5, 24, 256, 192, 16), (2, 300, 256, 256, 300),
+])
+def test_masked_matches_oracle(device, groups, max_m, n, k, expected_m):
+    import chord_b200
+
+    case = make_masked_case(groups, max_m, n, k, expected_m, seed=groups * 7 + max_m)
+    w = chord_b200.pack_w4a16(case["codes"].to(device), case["scale"].to(device))
+    out = torch.full((groups * max_m, n), float("nan"), dtype=torch.bfloat16, device=device)
+    res = chord_b200.masked(case["x3"].to(device), w, case["masked_m"].to(device), expected_m,
+                            outputs=out)
+    _status_ok(device)
+    assert res.shape == (groups * max_m, n) and res.data_ptr() == out.data_ptr()
+    ref = O.reference_masked(case["x3"], case["codes"], case["scale"], case["masked_m"])
+    _compare(out, ref.reshape(groups * max_m, n))
+
+
+def test_masked_ragged_groups_flat_input_and_repeatability(device):
+    """Ragged counts including empty and full groups, flat [G*max_m, K] input, int64
+    masked_m (cast like the reference does), three launches bit-equal."""
+    import chord_b200
+
+    groups, max_m, n, k = 48, 40, 256, 256
+    case = make_masked_case(groups, max_m, n, k, 8, seed=5)
+    case["masked_m"] = torch.tensor([(i * 7) % 41 for i in range(groups)], dtype=torch.int32)
+    w = chord_b200.pack_w4a16(case["codes"].to(device), case["scale"].to(device))
+    flat = case["x3"].reshape(groups * max_m, k).to(device)
+    outs = []
+    for _ in range(3):
+        out = torch.full((groups * max_m, n), float("nan"), dtype=torch.bfloat16, device=device)
+        chord_b200.masked(flat, w, case["masked_m"].long().to(device), 8, outputs=out)
+        outs.append(out)
+    _status_ok(device)
+    ref = O.reference_masked(case["x3"], case["codes"], case["scale"], case["masked_m"])
+    _compare(outs[0], ref.reshape(groups * max_m, n))
+    for other in outs[1:]:
+        assert torch.equal(other.view(torch.int16), outs[0].view(torch.int16))
+
+
+@pytest.mark.parametrize("counts,n,k,extra", [
+    ([128, 7, 300, 0, 129], 512, 512, 1), ([128] * 6, 256, 1024, 0), ([1], 128, 64, 0),
+    ([256, 512], 384, 2368, 0),
+])
+def test_contiguous_matches_oracle(device, counts, n, k, extra):
+    import chord_b200
+
+    case = make_contiguous_case(counts, n, k, seed=len(counts) + n, extra_padding_tiles=extra)
+    w = chord_b200.pack_w4a16(case["codes"].to(device), case["scale"].to(device))
+    m = case["x2"].size(0)
+    out = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device=device)
+    chord_b200.contiguous(case["x2"].to(device), w, case["m_indices"].to(device), outputs=out)
+    _status_ok(device)
+    ref = O.reference_contiguous(case["x2"], case["codes"], case["scale"], case["m_indices"])
+    _compare(out, ref)
+    # padding rows of a live tile come out as exact zeros (their inputs are zero)
+    got = out.float().cpu()
+    pad = (case["m_indices"] < 0) & ~torch.isnan(got).any(dim=1)
+    assert bool((got[pad] == 0).all())
+
+
+def test_one_packed_weight_serves_all_three_operators(device):
+    import chord_b200
+
+    e, n, k = 4, 256, 512
+    icase = make_indexed_case(num_experts=e, n=n, k=k, m=32, top_k=2, block_m=16, seed=40)
+    w = chord_b200.pack_w4a16(icase["codes"].to(device), icase["scale"].to(device))
+    locks = torch.zeros(1024, dtype=torch.int32, device=device)
+    out = torch.full((64, n), float("nan"), dtype=torch.bfloat16, device=device)
+    chord_b200.indexed(icase["x"].to(device), w, icase["sorted_ids"].to(device),
+                       icase["expert_ids"].to(device), icase["num_tokens_padded"].to(device).reshape(1),
+                       2, locks=locks, outputs=out, block_m=16)
+    ref = O.reference_indexed(icase["x"], icase["codes"], icase["scale"], icase["topk_ids"], 2)
+    _compare(out, ref)
+
+    g = torch.Generator().manual_seed(41)
+    x3 = torch.randn((e, 16, k), generator=g).to(torch.bfloat16)
+    mm = torch.tensor([16, 3, 0, 9], dtype=torch.int32)
+    out = torch.full((e * 16, n), float("nan"), dtype=torch.bfloat16, device=device)
+    chord_b200.masked(x3.to(device), w, mm.to(device), 8, outputs=out)
+    _compare(out, O.reference_masked(x3, icase["codes"], icase["scale"], mm).reshape(e * 16, n))
+
+    x2 = torch.randn((e * 128, k), generator=g).to(torch.bfloat16)
+    mi = torch.arange(e, dtype=torch.int32).repeat_interleave(128)
+    got = chord_b200.contiguous(x2.to(device), w, mi.to(device))
+    _compare(got, O.reference_contiguous(x2, icase["codes"], icase["scale"], mi))
+    _status_ok(device)
+
+
+def test_grouped_argument_checks(device):
+    import chord_b200
+
+    case = make_masked_case(2, 8, 128, 64, 8, seed=1)
+    w = chord_b200.pack_w4a16(case["codes"].to(device), case["scale"].to(device))
+    x3 = case["x3"].to(device)
+    mm = case["masked_m"].to(device)
+    with pytest.raises(ValueError, match="expected_m"):
+        chord_b200.masked(x3, w, mm, 0)
+    with pytest.raises(TypeError):
+        chord_b200.masked(x3, w, mm, 8.0)
+    with pytest.raises(ValueError, match="groups"):
+        chord_b200.masked(x3[:1].contiguous(), w, mm, 8)
+    with pytest.raises(ValueError, match="masked_m"):
+        chord_b200.masked(x3, w, mm[:1].contiguous(), 8)
+    with pytest.raises(ValueError, match="128-aligned"):
+        chord_b200.contiguous(x3.reshape(16, 64), w, torch.zeros(16, dtype=torch.int32, device=device))
+    with pytest.raises(ValueError, match="m_indices"):
+        chord_b200.contiguous(torch.zeros((128, 64), dtype=torch.bfloat16, device=device), w,
+                              torch.zeros(64, dtype=torch.int32, device=device))

@@ -1,0 +1,131 @@
+"""The CPU oracle against the golden vectors produced by the reference's own code
+(tests/golden/make_golden.py) and against itself (literal vs closed-form packer)."""
+
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import w4a16_oracle as O
+
+GOLDEN = Path(__file__).resolve().parent / "golden"
+
+
+def _bf16(bits: np.ndarray) -> torch.Tensor:
+    return torch.from_numpy(bits.copy()).view(torch.bfloat16)
+
+
+def _f32(bits: np.ndarray) -> torch.Tensor:
+    return torch.from_numpy(bits.copy()).view(torch.float32)
+
+
+def _load(name):
+    z = np.load(GOLDEN / f"{name}.npz")
+    e, n, k, m, top_k, block_m = (int(v) for v in z["shape"])
+    codes = torch.from_numpy(O.unpack_checkpoint_uint4(z["checkpoint"])).reshape(e, n, k)
+    return z, (e, n, k, m, top_k, block_m), codes
+
+
+@pytest.mark.parametrize("name", ["tiny", "mid"])
+def test_checkpoint_nibble_order_matches_reference(name):
+    z, (e, n, k, *_), codes = _load(name)
+    assert codes.min() >= 0 and codes.max() <= 15
+    assert np.array_equal(O.pack_checkpoint_uint4(codes.numpy()), z["checkpoint"])
+
+
+@pytest.mark.parametrize("name", ["tiny", "mid"])
+def test_scale_permutation_matches_reference(name):
+    z, _, _ = _load(name)
+    got = O.permute_scale(_bf16(z["scale"]))
+    assert torch.equal(got.view(torch.int16), torch.from_numpy(z["packed_scale"]))
+
+
+@pytest.mark.parametrize("name", ["tiny", "mid"])
+def test_routing_alignment_matches_reference(name):
+    z, (e, n, k, m, top_k, block_m), _ = _load(name)
+    topk = torch.from_numpy(z["topk_ids"])
+    sorted_ids, expert_ids, padded = O.align_routing_blocks(topk, block_m, e)
+    assert torch.equal(sorted_ids, torch.from_numpy(z["sorted_ids"]))
+    assert torch.equal(expert_ids, torch.from_numpy(z["expert_ids"]))
+    assert int(padded) == int(z["num_tokens_padded"])
+    # the same draw comes out of the oracle's generator
+    g = torch.Generator().manual_seed(m)
+    assert torch.equal(O.topk_ids_random(m, top_k, e, g), topk)
+
+
+@pytest.mark.parametrize("name", ["tiny", "mid"])
+@pytest.mark.parametrize("projection", ["gate_up", "down"])
+def test_indexed_reference_matches_reference(name, projection):
+    z, (e, n, k, m, top_k, block_m), codes = _load(name)
+    x = _bf16(z["x"] if projection == "gate_up" else z["x_routed"])
+    scale = _bf16(z["scale"])
+    topk = torch.from_numpy(z["topk_ids"])
+    want = _f32(z["ref_" + projection])
+    got = O.reference_indexed(x, codes, scale, topk, top_k, projection=projection)
+    # Same products, FP32 sums in a different order (einsum vs matmul).
+    assert O.max_abs_rel(got, want) < 1e-5
+    rowwise = O.reference_indexed_rowwise(x, codes, scale, topk, top_k, projection=projection)
+    assert O.max_abs_rel(rowwise, want) < 1e-6
+
+
+@pytest.mark.parametrize("name", ["tiny", "mid"])
+def test_fp32_dequant_matches_reference(name):
+    z, (e, n, k, *_), codes = _load(name)
+    got = O.dequant_reference_fp32(codes[0], _bf16(z["scale"])[0])
+    assert torch.equal(got, _f32(z["dequant_fp32_e0"]))
+    # and the BF16 dequantisation is its single rounding
+    assert torch.equal(O.dequantize_bf16(codes[0], _bf16(z["scale"])[0]), got.to(torch.bfloat16))
+
+
+def test_traffic_formula_matches_reference():
+    z, (e, n, k, m, top_k, _), _ = _load("mid")
+    assert O.traffic_bytes(e, n, k, m, m * top_k) == int(z["traffic"])
+    assert O.cosine_diff(_f32(z["ref_gate_up"]), _f32(z["ref_gate_up"])) == float(z["cos_self"])
+
+
+@pytest.mark.parametrize("shape", [(1, 64, 64), (2, 128, 128), (3, 192, 320)])
+def test_closed_form_packer_equals_literal_kernel_emulation(shape):
+    rng = np.random.default_rng(sum(shape))
+    codes = rng.integers(0, 16, size=shape, dtype=np.int32)
+    literal = O.repack_literal(codes)
+    closed = O.repack_closed_form(codes)
+    assert np.array_equal(literal, closed)
+    assert np.array_equal(O.unpack_closed_form(closed, shape[1], shape[2]), codes)
+
+
+def test_packed_word_layout_statement():
+    """One word: rows r and r+8, K offsets {2q, 2q+1, 2q+8, 2q+9}; low half-word = even K."""
+    codes = np.zeros((1, 64, 64), dtype=np.int32)
+    n, k = 16 * 2 + 8 * 1 + 5, 16 * 3 + 8 * 1 + 2 * 2 + 1   # s=2, rh=1, r8=5 ; kb=3, kh=1, q=2, kk=1
+    codes[0, n, k] = 0xF
+    packed = O.repack_closed_form(codes).view(np.uint32)
+    col = 4 * (4 * 5 + 2) + 2
+    assert packed[0, 3, col] == 0xF << (4 * (2 * 1 + 1) + 16)
+    assert np.count_nonzero(packed) == 1
+
+
+def test_routing_contract_properties():
+    g = torch.Generator().manual_seed(3)
+    topk = O.topk_ids_random(200, 8, 384, g)
+    for base, local in ((0, 48), (96, 48), (0, 384)):
+        for block_m in (8, 16, 64):
+            s, e, padded = O.align_routing_blocks(topk, block_m, local, base)
+            assert int(padded) == s.numel() and s.numel() % block_m == 0
+            valid = s[s < topk.numel()]
+            assert valid.numel() == valid.unique().numel()
+            want = ((topk.reshape(-1) >= base) & (topk.reshape(-1) < base + local)).sum()
+            assert valid.numel() == int(want)
+            blocks = s.view(-1, block_m) < topk.numel()
+            assert not (blocks & ((~blocks).cumsum(1) > 0)).any()      # valid prefix, then sentinels
+            assert blocks[:, 0].all()                                  # no empty block
+            owners = topk.reshape(-1)[s.view(-1, block_m)[:, 0].long()] - base
+            assert torch.equal(owners.to(torch.int32), e)
+
+
+def test_empty_routing_is_allowed():
+    topk = torch.full((4, 2), 300, dtype=torch.int32)
+    s, e, padded = O.align_routing_blocks(topk, 16, 48, 0)
+    assert s.numel() == 0 and e.numel() == 0 and int(padded) == 0
+    with pytest.raises(ValueError):
+        O.align_routing_blocks(topk, 16, 48, 0, allow_empty=False)
