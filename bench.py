@@ -27,7 +27,6 @@ from __future__ import annotations
 import argparse
 import json
 import os
-import subprocess
 import sys
 import threading
 import time
@@ -174,45 +173,56 @@ class DecodeWorkload:
 # --------------------------------------------------------------------- timing --
 
 class ClockSampler:
-    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
-
-    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
-             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
-             "clocks_event_reasons.sw_power_cap")
+    """Samples SM clock and throttle reasons (read-only NVML queries) in a background
+    thread while the timed region runs."""
 
     def __init__(self, index):
-        self.index, self.samples, self.proc = index, [], None
+        self.index, self.samples, self.reasons, self.max_mhz = index, [], 0, None
+        self.stop = threading.Event()
+        self.thread = None
 
     def __enter__(self):
         try:
-            self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.QUERY}",
-                 "--format=csv,noheader,nounits", "-lms", "100"],
-                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-            self.thread = threading.Thread(target=self._read, daemon=True)
+            import pynvml
+
+            pynvml.nvmlInit()
+            visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+            index = self.index
+            if visible:
+                entry = visible.split(",")[self.index].strip()
+                index = int(entry) if entry.isdigit() else self.index
+            handle = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = int(pynvml.nvmlDeviceGetMaxClockInfo(handle, pynvml.NVML_CLOCK_SM))
+
+            def poll():
+                while not self.stop.is_set():
+                    try:
+                        self.samples.append(int(pynvml.nvmlDeviceGetClockInfo(handle, pynvml.NVML_CLOCK_SM)))
+                        self.reasons |= int(pynvml.nvmlDeviceGetCurrentClocksEventReasons(handle))
+                    except Exception:
+                        break
+                    time.sleep(0.001)
+
+            self.thread = threading.Thread(target=poll, daemon=True)
             self.thread.start()
-        except OSError:
-            self.proc = None
+        except Exception:
+            self.thread = None
         return self
 
-    def _read(self):
-        for line in self.proc.stdout:
-            self.samples.append([c.strip() for c in line.split(",")])
-
     def __exit__(self, *exc):
-        if self.proc is not None:
-            self.proc.terminate()
+        self.stop.set()
+        if self.thread is not None:
             self.thread.join(timeout=2)
 
     def summary(self):
-        clocks = sorted(int(s[0]) for s in self.samples if s and s[0].isdigit())
-        if not clocks:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        reasons = [n for i, n in enumerate(names)
-                   if any(len(s) > 2 + i and s[2 + i].lower().startswith("active") for s in self.samples)]
-        return {"sm_mhz": clocks[len(clocks) // 2], "sm_max_mhz": int(self.samples[0][1]),
-                "reasons": reasons, "samples": len(clocks)}
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": [], "samples": 0}
+        bits = {"sw_power_cap": 0x4, "hw_slowdown": 0x8, "sw_thermal_slowdown": 0x20,
+                "hw_thermal_slowdown": 0x40}
+        clocks = sorted(self.samples)
+        return {"sm_mhz": clocks[len(clocks) // 2], "sm_max_mhz": self.max_mhz,
+                "reasons": [name for name, bit in bits.items() if self.reasons & bit],
+                "samples": len(clocks)}
 
 
 def barrier(world):
