@@ -34,6 +34,9 @@ SIGNATURES = {
     "chord_b200_schedule_segments": (_i64, [_i64, _i64, _i64, _i64, _ptr, _i64]),
     "chord_b200_indexed": (_int, [_ptr, _ptr, _ptr, _ptr, _i64, _ptr, _i64, _ptr, _ptr, _ptr, _i64,
                                   _ptr, _i64, _ptr, _i64, _i64, _i64, _i64, _i64, _i64, _ptr]),
+    "chord_b200_indexed_static_scratch": (_int, [_ptr, _ptr, _ptr, _ptr, _i64, _ptr, _i64, _ptr, _ptr,
+                                                 _ptr, _i64, _ptr, _i64, _i64, _i64, _i64, _i64, _i64,
+                                                 _ptr]),
     "chord_b200_contiguous": (_int, [_ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _i64, _ptr, _i64, _ptr,
                                      _i64, _i64, _i64, _i64, _ptr]),
     "chord_b200_masked": (_int, [_ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _i64, _ptr, _i64, _ptr,

@@ -222,6 +222,35 @@ int launch_gemm(GemmParams p, const void* x, const int32_t* packed, const void* 
   return launch_with_groups<2>(tm_w, tm_s, tm_x, p, grid, smem, s);
 }
 
+// Stream-K scratch that lives in the library image instead of in an allocation:
+// one FP32 slot of 128 x kStaticScratchTokens per CTA for up to kStaticScratchCtas
+// CTAs (5 MiB).  Every GPU that loads the library holds it until the process exits.
+constexpr int kStaticScratchTokens = 64;
+constexpr int kStaticScratchCtas = 160;
+static __device__ __align__(256) float
+    static_stream_k_scratch[kStaticScratchCtas * kBlockN * kStaticScratchTokens];
+
+// Device address of the array above on the current device.  In host code the array's
+// name is only a handle for the runtime, not an address a kernel could use, so the
+// address is looked up once per device (with that device current) and remembered.
+int static_scratch_address(float** out) {
+  constexpr int kMaxDevices = 64;
+  static std::mutex mutex;
+  static float* address[kMaxDevices] = {};
+  int device = 0;
+  CHORD_CUDA(cudaGetDevice(&device));
+  if (device < 0 || device >= kMaxDevices) return fail(kCudaError, "device index %d out of range", device);
+  std::lock_guard<std::mutex> guard(mutex);
+  if (address[device] == nullptr) {
+    void* ptr = nullptr;
+    CHORD_CUDA(cudaGetSymbolAddress(&ptr, static_stream_k_scratch));
+    if (ptr == nullptr) return fail(kCudaError, "cudaGetSymbolAddress returned a null address");
+    address[device] = static_cast<float*>(ptr);
+  }
+  *out = address[device];
+  return kOk;
+}
+
 }  // namespace
 }  // namespace chord
 
@@ -328,6 +357,35 @@ int chord_b200_indexed(const void* x, const int32_t* packed, const void* scale,
   p.locks = locks;
   p.status = status;
   return chord::launch_gemm(p, x, packed, scale, num_locks, workspace_bytes, stream);
+}
+
+int chord_b200_indexed_static_scratch(const void* x, const int32_t* packed, const void* scale,
+                                      const int32_t* sorted_ids, int64_t sorted_len,
+                                      const int32_t* expert_ids, int64_t expert_len,
+                                      const int32_t* num_tokens_padded, void* out, int32_t* locks,
+                                      int64_t num_locks, int32_t* status, int64_t m, int64_t n,
+                                      int64_t k, int64_t num_experts, int64_t top_k,
+                                      int64_t block_m, void* stream) {
+  CHORD_REQUIRE(block_m > 0 && block_m <= chord::kStaticScratchTokens,
+                "the built-in scratch holds token blocks of at most %d rows, got block_m=%lld; "
+                "use chord_b200_indexed with a caller-provided workspace for larger blocks",
+                chord::kStaticScratchTokens, static_cast<long long>(block_m));
+  chord::DeviceInfo dev;
+  if (int rc = chord::current_device_info(&dev)) return rc;
+  const int grid = chord::grid_size(dev);
+  CHORD_REQUIRE(grid <= chord::kStaticScratchCtas,
+                "the built-in scratch serves at most %d CTAs, this GPU would launch %d; "
+                "use chord_b200_indexed with a caller-provided workspace",
+                chord::kStaticScratchCtas, grid);
+  float* scratch = nullptr;
+  if (int rc = chord::static_scratch_address(&scratch)) return rc;
+  const int64_t scratch_bytes = static_cast<int64_t>(chord::kStaticScratchCtas) * chord::kBlockN *
+                                chord::kStaticScratchTokens * 4;
+  // Nothing in the scratch has to start at zero: a slot is written in full by the CTA
+  // that owns it before the reducing CTA reads it, so the last call's contents are harmless.
+  return chord_b200_indexed(x, packed, scale, sorted_ids, sorted_len, expert_ids, expert_len,
+                            num_tokens_padded, out, locks, num_locks, scratch, scratch_bytes, status,
+                            m, n, k, num_experts, top_k, block_m, stream);
 }
 
 int chord_b200_contiguous(const void* x, const int32_t* packed, const void* scale,

@@ -112,6 +112,32 @@ int chord_b200_indexed(const void* x, const int32_t* packed, const void* scale,
                        int32_t* status, int64_t m, int64_t n, int64_t k, int64_t num_experts,
                        int64_t top_k, int64_t block_m, void* stream);
 
+/* ---- indexed GEMM without a workspace argument ---------------------------------
+ * No counterpart in the reference (its launcher always takes the stream-K scratch
+ * from torch's allocator).  Same operation and arguments as chord_b200_indexed, but
+ * the FP32 stream-K scratch is a fixed 5 MiB array inside the library image, so the
+ * call allocates nothing on the device.  It is meant for hosts that must not call
+ * cudaMalloc on the request path: a serving loop whose memory pool is sized and
+ * frozen at start-up, a plugin running inside another process's CUDA context whose
+ * allocator it may not touch, or code between the begin and end of a region in which
+ * allocation is forbidden.
+ *  - Limits: block_m <= 64 and at most 160 CTAs (one per SM); anything larger is
+ *    refused with return code 1 and a message naming the limit.
+ *  - The first call on each device looks up the array's device address
+ *    (cudaGetSymbolAddress, once per device); make that first call outside any
+ *    stream capture.
+ *  - All calls on a device share the one array: calls that may overlap on the GPU
+ *    (different streams without ordering) race on it, exactly as calls sharing
+ *    `locks` do.  Nothing in it needs clearing between calls.
+ *  - Every GPU that loads the library keeps the 5 MiB until the process exits. */
+int chord_b200_indexed_static_scratch(const void* x, const int32_t* packed, const void* scale,
+                                      const int32_t* sorted_ids, int64_t sorted_len,
+                                      const int32_t* expert_ids, int64_t expert_len,
+                                      const int32_t* num_tokens_padded, void* out, int32_t* locks,
+                                      int64_t num_locks, int32_t* status, int64_t m, int64_t n,
+                                      int64_t k, int64_t num_experts, int64_t top_k,
+                                      int64_t block_m, void* stream);
+
 /* ---- contiguous GEMM: replaces launch_grouped_w4a16_contiguous
  * (launcher.cpp:505-549) --------------------------------------------------------
  * out[r, :] = x[r, :] . dequant(W[m_indices[tile first row]])^T for every 128-row
