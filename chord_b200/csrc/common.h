@@ -64,6 +64,7 @@ struct Options {
   int x_load = 0;          // indexed activation gather: 0 = cp.async helper warps, 1 = TMA gather4
   int dequant_groups = 2;  // 2 or 4 groups of four dequant warps
   int issuers = 0;         // 0 = automatic; 1, 2 or 4 MMA issuers
+  int a_stages = 0;        // 0 = automatic; depth of the TMEM operand ring (2..7)
   int max_stages = 0;      // 0 = as many as fit
   int grid_limit = 0;      // 0 = one CTA per SM
   int ablate = 0;          // CHORD_PROFILE builds: bit mask of work to skip in timing studies

@@ -74,6 +74,9 @@ int chord_b200_set_option(const char* name, int64_t value) {
     if (value != 0 && value != 1 && value != 2 && value != 4)
       return fail(kInvalidArgument, "issuers must be 0, 1, 2 or 4");
     o.issuers = static_cast<int>(value);
+  } else if (!std::strcmp(name, "a_stages")) {
+    if (value != 0 && (value < 2 || value > 7)) return fail(kInvalidArgument, "a_stages must be 0 or 2..7");
+    o.a_stages = static_cast<int>(value);
   } else if (!std::strcmp(name, "max_stages")) {
     if (value < 0 || value > 64) return fail(kInvalidArgument, "max_stages must be in [0, 64]");
     o.max_stages = static_cast<int>(value);

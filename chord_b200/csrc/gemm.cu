@@ -180,10 +180,29 @@ int launch_gemm(GemmParams p, const void* x, const int32_t* packed, const void* 
                 p.tile_tokens);
   // Consecutive rows take one tiled box per K half; routed rows are gathered.
   // Small token tiles are issue-bound with one MMA issuer: use one per dequant group.
+  // The accumulators (issuers x buffers x mma_n columns, double-buffered where they
+  // fit) take 128 of the 512 TMEM columns for decode-sized tiles and 256 otherwise;
+  // the dequantised-operand ring gets the rest.
   const int groups = options().dequant_groups == 4 ? 4 : 2;
-  // Keep the accumulators double-buffered (2 * issuers * mma_n <= 256 columns) where possible.
-  p.issuers = p.mma_n <= 32 ? groups : (p.mma_n <= 64 ? 2 : 1);
+  p.issuers = p.mma_n <= 16 ? groups : (p.mma_n <= 64 ? 2 : 1);
   if (options().issuers > 0 && options().issuers * p.mma_n <= 256) p.issuers = options().issuers;
+  const int acc_cols = p.issuers * p.mma_n;
+  p.a_stages = 2 * acc_cols <= 128 ? 6 : 4;
+  if (options().a_stages > 0 && (512 - 64 * options().a_stages) >= acc_cols) {
+    p.a_stages = options().a_stages;
+  }
+  // Ring depths are multiples of the number of warp groups (or issuers) that take
+  // turns on a ring, so that successive uses of one barrier are always awaited by the
+  // same threads in program order.  Otherwise a party that runs ahead could ask for
+  // phase u+1 of a barrier still in phase u-1 and be let through (mbarrier waits only
+  // know the phase parity).
+  const int turn = groups > p.issuers ? groups : p.issuers;  // both are powers of two
+  p.a_stages -= p.a_stages % turn;
+  p.w_stages -= p.w_stages % groups;
+  p.x_stages -= p.x_stages % p.issuers;
+  CHORD_REQUIRE(p.a_stages >= turn && p.w_stages >= groups && p.x_stages >= p.issuers,
+                "internal: ring depths %d/%d/%d too small for %d groups and %d issuers",
+                p.a_stages, p.w_stages, p.x_stages, groups, p.issuers);
   p.x_load = p.mode == kModeIndexed ? (options().x_load == 1 ? kXLoadGather4 : kXLoadCpAsync)
                                     : kXLoadTiled;
   p.profile = reinterpret_cast<unsigned long long*>(options().profile_buffer);

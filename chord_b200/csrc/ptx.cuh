@@ -83,28 +83,47 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 
 // Bounded wait.  `abort_flag` is a shared-memory word any role may set when it
 // gives up; once set, every other waiter leaves too.  Returns false on
-// timeout (about two seconds of SM clock) or abort.
+// timeout (about two seconds of SM clock) or abort.  The common case - the phase
+// has already completed - costs one try and one branch; everything else is kept
+// out of line so that the hot loops stay short.
 constexpr long long kWaitTimeoutCycles = 4000000000ll;
 
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity,
-                                          volatile uint32_t* abort_flag) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const long long start = clock64();
-  for (uint32_t spin = 1;; ++spin) {
+__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity,
+                                            volatile uint32_t* abort_flag) {
+  // A few immediate retries for waits that are about to end, then sleep between
+  // tries: some twenty warps per CTA wait most of the time, and a polling loop that
+  // never yields would take the issue slots the working warps need.
+  for (uint32_t spin = 0; spin < 4; ++spin) {
     if (mbar_try_wait(bar, parity)) return true;
-    if ((spin & 0x3) == 0) {
+  }
+  const long long start = clock64();
+  uint32_t sleep_ns = 32;
+  for (uint32_t spin = 1;; ++spin) {
+    __nanosleep(sleep_ns);
+    if (mbar_try_wait(bar, parity)) return true;
+    if (sleep_ns < 256) sleep_ns <<= 1;
+    if ((spin & 0x3f) == 0) {
       if (*abort_flag != 0) return false;
       if (clock64() - start > kWaitTimeoutCycles) return false;
     }
   }
 }
 
-// Warp-uniform form: every lane waits (each needs the acquire), and the warp
-// agrees on the outcome so that a timeout never splits it.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity,
+                                          volatile uint32_t* abort_flag) {
+  if (mbar_try_wait(bar, parity)) return true;
+  return mbar_wait_slow(bar, parity, abort_flag);
+}
+
+// Warp-uniform form: every lane waits (each needs the acquire).  A warp executes the
+// try as one instruction on one address, so its first outcome is the same in every
+// lane; only the slow path can end differently per lane, and there the warp votes so
+// that a timeout never splits it.
 __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity,
                                                volatile uint32_t* abort_flag) {
-  const bool ok = mbar_wait(bar, parity, abort_flag);
-  return __all_sync(0xffffffffu, ok);
+  if (mbar_try_wait(bar, parity)) return true;
+  const bool ok = mbar_wait_slow(bar, parity, abort_flag);
+  return __all_sync(__activemask(), ok);
 }
 
 // --------------------------------------------------------------------- TMA --

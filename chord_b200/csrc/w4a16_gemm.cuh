@@ -108,13 +108,15 @@ constexpr int kBlockN = 128;      // weight rows per tile (MMA M)
 constexpr int kBlockK = 128;      // K elements per pipeline stage (two 64-wide swizzle atoms)
 constexpr int kMaxWStages = 24;   // ring of packed-weight + scale stages
 constexpr int kMaxXStages = 8;    // ring of activation stages
-// Tensor-memory ring for the dequantised A operand: eight slots of one 64-wide K
-// half (32 columns) each.  Stage `it` uses slots 2 (it % 4) and 2 (it % 4) + 1, so
-// that the MMAs of a stage's first half are issued while its second half is still
-// being dequantised.
-constexpr int kASlots = 8;
-constexpr int kAColsPerSlot = 32;
-constexpr int kDCol0 = kASlots * kAColsPerSlot;  // 256
+// Tensor-memory ring for the dequantised A operand: `a_stages` stages of 64 columns,
+// each handed over in two halves of one 64-wide K half (32 columns), so that the
+// MMAs of a stage's first half are issued while its second half is still being
+// dequantised.  The ring takes the columns the accumulators leave free (4 stages next
+// to 256 accumulator columns, 6 next to 128): the deeper it is, the further the
+// dequant warps run ahead of the MMA issuers, which hides the barrier round trips
+// between them.
+constexpr int kMaxAStages = 8;
+constexpr int kAColsPerStage = kBlockK / 2;
 constexpr int kHelperThreads = 64;  // warps 2-3: activation gather for `indexed`
 constexpr int kTmemCols = 512;
 constexpr int kMaxTileTokens = 256;
@@ -140,6 +142,7 @@ struct GemmParams {
   int32_t w_stages;     // depth of the weight/scale ring
   int32_t x_stages;     // depth of the activation ring
   int32_t issuers;      // 1, 2 or 4 MMA issuers (and accumulators)
+  int32_t a_stages;     // depth of the TMEM A ring; accumulators start at column 64 * a_stages
   int32_t num_locks;
   const int32_t* sorted_ids;
   const int32_t* expert_ids;
@@ -246,8 +249,8 @@ struct __align__(16) GemmShared {
   uint64_t wempty[kMaxWStages];  // dequant warps have read them   (4 arrivals)
   uint64_t xfull[kMaxXStages];   // activations landed
   uint64_t xempty[kMaxXStages];  // the stage's MMAs have completed (1 commit)
-  uint64_t afull[kASlots];
-  uint64_t aempty[kASlots];
+  uint64_t afull[2 * kMaxAStages];   // per K half: dequantised operand stored (4 arrivals)
+  uint64_t aempty[2 * kMaxAStages];  // per K half: its MMAs have completed (1 commit)
   uint64_t dfull[2];
   uint64_t dempty[2];
   uint32_t tmem_base;
@@ -362,6 +365,14 @@ struct StageCursor {
       ph ^= 1u;
     }
   }
+  // Any distance, without a division (a few subtractions per tile at most).
+  __device__ __forceinline__ void advance_by(uint32_t n, uint32_t stages) {
+    s += n;
+    while (s >= stages) {
+      s -= stages;
+      ph ^= 1u;
+    }
+  }
 };
 
 template <int kDequantGroups>
@@ -390,10 +401,12 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
   constexpr uint32_t kFirstEpilogueWarp = 8 + 4 * kDequantGroups;
   // Accumulators: `ni` issuers x `d_bufs` buffers of `d_cols` columns each in the
   // 256 TMEM columns after the A ring; buffer d of issuer i starts at column
-  // kDCol0 + (d * ni + i) * d_cols.
+  // 64 * a_stages + (d * ni + i) * d_cols.
   const uint32_t ni = static_cast<uint32_t>(p.issuers);
   const uint32_t d_cols = static_cast<uint32_t>(p.mma_n);
-  const uint32_t d_bufs = 2u * ni * d_cols <= 256u ? 2u : 1u;
+  const uint32_t a_stages = static_cast<uint32_t>(p.a_stages);
+  const uint32_t d_col0 = a_stages * kAColsPerStage;
+  const uint32_t d_bufs = 2u * ni * d_cols <= kTmemCols - d_col0 ? 2u : 1u;
   const int32_t k_iters = (p.k + kBlockK - 1) / kBlockK;
   const bool k_tail_half = (p.k % kBlockK) != 0;  // last stage carries 64 K values only
 
@@ -412,7 +425,7 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
       ptx::mbar_init(ptx::smem_u32(&sh.xfull[s]), xfull_count);
       ptx::mbar_init(ptx::smem_u32(&sh.xempty[s]), 1);
     }
-    for (uint32_t a = 0; a < kASlots; ++a) {
+    for (uint32_t a = 0; a < 2 * a_stages; ++a) {
       ptx::mbar_init(ptx::smem_u32(&sh.afull[a]), 4);
       ptx::mbar_init(ptx::smem_u32(&sh.aempty[a]), 1);
     }
@@ -695,7 +708,7 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
       const uint64_t xdesc_stage = x_stage_bytes >> 4;  // descriptor address units are 16 bytes
       const uint64_t xdesc_half = x_half_bytes >> 4;
       uint64_t xdesc = xdesc0;
-      StageCursor cur;
+      StageCursor cur, acur;
       uint32_t it = 0, segc = 0;
       bool ok = true;
       CHORD_PROF_INIT();
@@ -711,12 +724,12 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
         }
         CHORD_PROF_ADD(1, pt0);
         ptx::tc_fence_after();
-        const uint32_t d_addr = tmem_base + kDCol0 + (d * ni + me) * d_cols;
+        const uint32_t d_addr = tmem_base + d_col0 + (d * ni + me) * d_cols;
         uint32_t acc = 0;
         for (int32_t kb = seg.kb; kb < seg.ke; ++kb, ++it) {
           if ((it & (ni - 1)) == me) {
-            const uint32_t a = (it & 3u) << 1;  // slot of the first K half; the second is a + 1
-            const uint32_t aph = (it >> 2) & 1u;
+            const uint32_t a = acur.s << 1;  // barrier of the first K half; the second is a + 1
+            const uint32_t aph = acur.ph;
             CHORD_PROF_T(pt1);
             if (!CHORD_ABLATE(4) &&
                 !ptx::mbar_wait(ptx::smem_u32(&sh.xfull[cur.s]), cur.ph, abort_flag)) {
@@ -733,7 +746,7 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
             CHORD_PROF_ADD(3, pt2);
             CHORD_PROF_T(pt3);
             ptx::tc_fence_after();
-            const uint32_t a_addr = tmem_base + a * kAColsPerSlot;
+            const uint32_t a_addr = tmem_base + acur.s * kAColsPerStage;
             if (!CHORD_ABLATE(0)) {
               ptx::mma_ts(d_addr, a_addr, xdesc, idesc, acc);
               ptx::mma_ts(d_addr, a_addr + 8, xdesc + 2, idesc, 1);
@@ -764,6 +777,7 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
           }
           xdesc += xdesc_stage;
           cur.advance(x_stages);
+          acur.advance(a_stages);
           if (cur.s == 0) xdesc = xdesc0;
         }
         if (!ok) break;
@@ -787,7 +801,7 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
     // 64-row chunk q>>1) inside one K16 row of the stage, and of its four scales.
     const uint32_t w_off = (q >> 1) * 512u + lane * 16u + (q & 1) * 8u;
     const uint32_t s_off = (q >> 1) * 128u + (lane >> 2) * 16u + (q & 1) * 8u;
-    StageCursor cur;
+    StageCursor cur, acur;
     uint32_t it = 0;
     bool ok = true;
     // A stored K half is published to the MMA issuer one compute step later (after
@@ -843,7 +857,7 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
                           const uint32_t (&hi)[16]) -> bool {
       if (!ptx::mbar_wait_warp(ptx::smem_u32(&sh.aempty[slot]), aph ^ 1u, abort_flag)) return false;
       ptx::tc_fence_after();
-      const uint32_t a_addr = tmem_base + ((q * 32u) << 16) + slot * kAColsPerSlot;
+      const uint32_t a_addr = tmem_base + ((q * 32u) << 16) + slot * (kAColsPerStage / 2);
       if (!CHORD_ABLATE(2)) {
         ptx::tmem_st_16x128b_x8(a_addr, lo);
         ptx::tmem_st_16x128b_x8(a_addr + (16u << 16), hi);
@@ -857,10 +871,24 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
     while (ok && iter.next(seg)) {
       const TileInfo t = decode_tile(p, sh, seg.tile);
       if (!t.valid) continue;
-      for (int32_t kb = seg.kb; kb < seg.ke; ++kb, ++it, cur.advance(w_stages)) {
-        if ((it & (kDequantGroups - 1)) != group) continue;
-        const uint32_t a = (it & 3u) << 1;  // slots a (first K half) and a + 1 (second)
-        const uint32_t aph = (it >> 2) & 1u;
+      // This group owns the stages whose running index is `group` modulo the number
+      // of groups: step over the others without visiting them.
+      const uint32_t seg_len = static_cast<uint32_t>(seg.ke - seg.kb);
+      const uint32_t first = (group - it) & (kDequantGroups - 1);
+      const uint32_t it_end = it + seg_len;
+      if (first >= seg_len) {
+        it = it_end;
+        cur.advance_by(seg_len, w_stages);
+        acur.advance_by(seg_len, a_stages);
+        continue;
+      }
+      it += first;
+      cur.advance_by(first, w_stages);
+      acur.advance_by(first, a_stages);
+      for (; it < it_end; it += kDequantGroups, cur.advance_by(kDequantGroups, w_stages),
+                          acur.advance_by(kDequantGroups, a_stages)) {
+        const uint32_t a = acur.s << 1;  // half-slots a (first K half) and a + 1 (second)
+        const uint32_t aph = acur.ph;
         CHORD_PROF_T(pt0);
         if (!ptx::mbar_wait_warp(ptx::smem_u32(&sh.wfull[cur.s]), cur.ph, abort_flag)) {
           ok = false;
@@ -897,6 +925,15 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
           break;
         }
         CHORD_PROF_ADD(4, pt4);
+      }
+      // `it` overshoots the segment's end by less than one stride: bring the cursor back.
+      if (ok) {
+        const uint32_t over = it - it_end;
+        it = it_end;
+        cur.advance_by(w_stages - over, w_stages);
+        cur.ph ^= 1u;
+        acur.advance_by(a_stages - over, a_stages);
+        acur.ph ^= 1u;
       }
     }
     publish();
@@ -947,7 +984,7 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
       }
       CHORD_PROF_ADD(1, pt0);
       CHORD_PROF_T(pt1);
-      const uint32_t d_addr = tmem_base + ((q * 32u) << 16) + kDCol0 + d * ni * d_cols;
+      const uint32_t d_addr = tmem_base + ((q * 32u) << 16) + d_col0 + d * ni * d_cols;
       __nv_bfloat16* out_col = p.out + t.n0 + et;
       // Issuer i accumulated the stages it0 + j with (it0 + j) % ni == i; it took part
       // in this segment only if one of them falls inside it.

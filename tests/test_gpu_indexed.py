@@ -134,6 +134,24 @@ def test_deterministic_and_locks_reused(device):
     check_against_oracle(outs[0], case)
 
 
+@pytest.mark.parametrize("groups", [2, 4])
+def test_repeatable_with_every_group_count(device, groups):
+    """Ten launches, stream-K on every tile, 2 and 4 dequant groups (which also changes
+    the number of MMA issuers and the depth of the operand ring): bit-equal every time.
+    Guards the rule that ring depths are multiples of the parties taking turns on them."""
+    from chord_b200 import _lib
+
+    case = make_indexed_case(num_experts=6, n=512, k=7168, m=12, top_k=2, block_m=16, seed=26)
+    _lib.set_option("dequant_groups", groups)
+    try:
+        outs = [run_case(device, case)[0].clone() for _ in range(10)]
+    finally:
+        _lib.set_option("dequant_groups", 2)
+    check_against_oracle(outs[0], case)
+    for other in outs[1:]:
+        assert torch.equal(other.view(torch.int16), outs[0].view(torch.int16))
+
+
 def test_stream_k_split_matches_whole_tiles(device):
     """Few tiles on many CTAs forces every tile through the stream-K reduction; a
     one-CTA grid computes whole tiles.  FP32 partials summed once: nearly all outputs
