@@ -64,6 +64,7 @@ struct Options {
   int x_load = 0;          // indexed activation gather: 0 = cp.async helper warps, 1 = TMA gather4
   int dequant_groups = 2;  // 2 or 4 groups of four dequant warps
   int issuers = 0;         // 0 = automatic; 1, 2 or 4 MMA issuers
+  int contiguous_tile = 0; // 0 / 256 = merge neighbouring 128-row blocks of one expert; 128 = do not
   int a_stages = 0;        // 0 = automatic; depth of the TMEM operand ring (2..7)
   int max_stages = 0;      // 0 = as many as fit
   int grid_limit = 0;      // 0 = one CTA per SM

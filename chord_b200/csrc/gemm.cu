@@ -166,6 +166,8 @@ int launch_gemm(GemmParams p, const void* x, const int32_t* packed, const void* 
                 "token tile %d must be in [1, %d]", p.tile_tokens, kMaxTileTokens);
   CHORD_REQUIRE(x != nullptr && packed != nullptr && scale != nullptr && p.out != nullptr,
                 "null tensor pointer");
+  CHORD_REQUIRE((reinterpret_cast<uintptr_t>(p.out) & 15u) == 0,
+                "the output tensor must be 16-byte aligned");
   CHORD_REQUIRE(static_cast<int64_t>(p.num_experts) * (p.k / 16) < (1ll << 31) &&
                     static_cast<int64_t>(p.x_rows) < (1ll << 31) - 1,
                 "tensor too large for 32-bit TMA coordinates");
@@ -216,6 +218,7 @@ int launch_gemm(GemmParams p, const void* x, const int32_t* packed, const void* 
                 "workspace must hold %lld bytes, got %lld", static_cast<long long>(need),
                 static_cast<long long>(workspace_bytes));
 
+  p.x_box_rows = p.mode == kModeContiguous ? 128 : p.mma_n;
   CUtensorMap tm_w, tm_s, tm_x;
   if (int rc = make_map_2d(&tm_w, packed, CU_TENSOR_MAP_DATA_TYPE_INT32, 4,
                            static_cast<uint64_t>(p.n) * 2,
@@ -229,7 +232,7 @@ int launch_gemm(GemmParams p, const void* x, const int32_t* packed, const void* 
     return rc;
   if (int rc = make_map_2d(&tm_x, x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
                            static_cast<uint64_t>(p.k), static_cast<uint64_t>(p.x_rows), 64,
-                           p.x_load == kXLoadTiled ? static_cast<uint32_t>(p.mma_n) : 1u,
+                           p.x_load == kXLoadTiled ? static_cast<uint32_t>(p.x_box_rows) : 1u,
                            CU_TENSOR_MAP_SWIZZLE_128B))
     return rc;
 
@@ -422,7 +425,11 @@ int chord_b200_contiguous(const void* x, const int32_t* packed, const void* scal
   p.num_experts = static_cast<int32_t>(num_experts);
   p.x_rows = static_cast<int32_t>(m);
   p.out_rows = static_cast<int32_t>(m);
-  p.tile_tokens = 128;
+  CHORD_REQUIRE(m / 128 <= chord::kMaxMTiles && num_experts <= 0x7FFF,
+                "contiguous supports at most %d rows and %d experts", chord::kMaxMTiles * 128, 0x7FFF);
+  // Token tiles are 128-row blocks, merged in pairs where two neighbours belong to one
+  // expert (option contiguous_tile = 128 switches the merging off).
+  p.tile_tokens = chord::options().contiguous_tile == 128 ? 128 : 256;
   p.top_k = 1;
   p.m_blocks = static_cast<int32_t>(m / 128);
   p.m_indices = m_indices;

@@ -121,6 +121,7 @@ constexpr int kHelperThreads = 64;  // warps 2-3: activation gather for `indexed
 constexpr int kTmemCols = 512;
 constexpr int kMaxTileTokens = 256;
 constexpr int kMaxGroups = 512;   // masked: prefix table capacity
+constexpr int kMaxMTiles = 2048;  // contiguous: 128-row blocks of the activation tensor
 constexpr int kWStageBytes = (kBlockK / 16) * 1024;
 constexpr int kSStageBytes = (kBlockK / 32) * 256;
 
@@ -137,6 +138,7 @@ struct GemmParams {
   int32_t top_k;        // indexed
   int32_t max_m;        // masked
   int32_t m_blocks;     // contiguous: m / 128
+  int32_t x_box_rows;   // tiled activation loads: rows per TMA box
   int32_t sorted_len;   // indexed: capacity of sorted_ids
   int32_t expert_len;   // indexed: capacity of expert_ids
   int32_t w_stages;     // depth of the weight/scale ring
@@ -165,6 +167,7 @@ struct TileInfo {
   int32_t base;    // indexed: first sorted_ids slot; contiguous: first row; masked: first row of the group
   int32_t m0;      // masked: first row inside the group
   int32_t limit;   // masked: masked_m of the group
+  int32_t mma_n;   // MMA N of this tile (contiguous tiles are 128 or 256 tokens)
   bool valid;
 };
 
@@ -259,8 +262,12 @@ struct __align__(16) GemmShared {
   volatile uint32_t epilogue_failed;
   int32_t x_slots;                   // helpers: token slots of the current tile that carry a row
   int32_t out_row[kMaxTileTokens];   // epilogue: output row per token slot, -1 = skip
+  __align__(16) __nv_bfloat16 stage[4][16][32];  // epilogue: per-warp transpose buffer
   int32_t x_row[kMaxTileTokens];     // producer (cp.async variant): activation row per slot
   int32_t group_prefix[kMaxGroups + 1];  // masked: first M tile of each group
+  // contiguous: M tiles after merging neighbouring 128-row blocks of one expert:
+  // expert | first block << 15 | (256 rows ? 1 : 0) << 31
+  uint32_t mtile[kMaxMTiles];
 };
 
 __device__ __forceinline__ TileInfo decode_tile(const GemmParams& p, const GemmShared& sh,
@@ -271,14 +278,17 @@ __device__ __forceinline__ TileInfo decode_tile(const GemmParams& p, const GemmS
   t.n0 = (tile - mb * n_blocks) * kBlockN;
   t.m0 = 0;
   t.limit = 0;
+  t.mma_n = p.mma_n;
   if (p.mode == kModeIndexed) {
     t.expert = __ldg(p.expert_ids + mb);
     t.ntok = p.tile_tokens;
     t.base = mb * p.tile_tokens;
   } else if (p.mode == kModeContiguous) {
-    t.expert = __ldg(p.m_indices + mb * p.tile_tokens);
-    t.ntok = p.tile_tokens;
-    t.base = mb * p.tile_tokens;
+    const uint32_t info = sh.mtile[mb];
+    t.expert = static_cast<int32_t>(info & 0x7FFFu);
+    t.ntok = (info >> 31) ? 256 : 128;
+    t.mma_n = t.ntok;
+    t.base = static_cast<int32_t>((info >> 15) & 0xFFFFu) * 128;
   } else {
     // Largest g with group_prefix[g] <= mb.
     int32_t lo = 0, hi = p.num_experts;
@@ -466,7 +476,30 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
       sh.m_blocks = blocks > p.expert_len ? p.expert_len : blocks;
     }
   } else {
-    if (threadIdx.x == 0) sh.m_blocks = p.m_blocks;
+    // Expert of every 128-row block (its first row names it), then one thread merges
+    // neighbouring blocks of one expert into 256-token tiles (the MMA runs at full
+    // rate only with N = 256) and drops padding blocks.  In place: the write position
+    // never passes the read position.
+    for (int32_t i = threadIdx.x; i < p.m_blocks; i += blockDim.x) {
+      sh.mtile[i] = static_cast<uint32_t>(__ldg(p.m_indices + i * 128));
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      int32_t count = 0;
+      for (int32_t i = 0; i < p.m_blocks;) {
+        const int32_t e = static_cast<int32_t>(sh.mtile[i]);
+        if (e < 0 || e >= p.num_experts) {
+          ++i;
+          continue;
+        }
+        const bool pair = p.tile_tokens == 256 && i + 1 < p.m_blocks &&
+                          static_cast<int32_t>(sh.mtile[i + 1]) == e;
+        sh.mtile[count++] = static_cast<uint32_t>(e) | (static_cast<uint32_t>(i) << 15) |
+                            (pair ? 0x80000000u : 0u);
+        i += pair ? 2 : 1;
+      }
+      sh.m_blocks = count;
+    }
   }
   ptx::fence_proxy_async();
   ptx::tc_fence_before();
@@ -506,8 +539,12 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
           CHORD_PROF_ADD(1, pt0);
           CHORD_PROF_T(pt1);
           const uint32_t full = ptx::smem_u32(&sh.wfull[cur.s]);
-          ptx::mbar_arrive_expect_tx(full, stage_bytes);
-          ptx::tma_load_2d(ptx::smem_u32(ring + cur.s * stage_bytes), map, full, col, row);
+          if (CHORD_ABLATE(5) && !weights) {
+            ptx::mbar_arrive(full);
+          } else {
+            ptx::mbar_arrive_expect_tx(full, stage_bytes);
+            ptx::tma_load_2d(ptx::smem_u32(ring + cur.s * stage_bytes), map, full, col, row);
+          }
           row += rows_per_stage;
           cur.advance(w_stages);
           CHORD_PROF_ADD(2, pt1);
@@ -532,6 +569,7 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
         if (!t.valid) continue;
         int32_t k_col = seg.kb * kBlockK;
         const int32_t x_row0 = t.base + t.m0;
+        const int32_t boxes = (t.mma_n + p.x_box_rows - 1) / p.x_box_rows;
         for (int32_t kb = seg.kb; kb < seg.ke; ++kb) {
           if (!ptx::mbar_wait(ptx::smem_u32(&sh.xempty[cur.s]), cur.ph ^ 1u, abort_flag)) {
             ok = false;
@@ -539,9 +577,13 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
           }
           const uint32_t full = ptx::smem_u32(&sh.xfull[cur.s]);
           const uint32_t xs = ptx::smem_u32(smem_x + cur.s * x_stage_bytes);
-          ptx::mbar_arrive_expect_tx(full, x_stage_bytes);
-          ptx::tma_load_2d(xs, &tm_x, full, k_col, x_row0);
-          ptx::tma_load_2d(xs + x_half_bytes, &tm_x, full, k_col + 64, x_row0);
+          ptx::mbar_arrive_expect_tx(full, static_cast<uint32_t>(boxes * p.x_box_rows) * 256u);
+          for (int32_t b = 0; b < boxes; ++b) {
+            const uint32_t off = static_cast<uint32_t>(b * p.x_box_rows) * 128u;
+            ptx::tma_load_2d(xs + off, &tm_x, full, k_col, x_row0 + b * p.x_box_rows);
+            ptx::tma_load_2d(xs + x_half_bytes + off, &tm_x, full, k_col + 64,
+                             x_row0 + b * p.x_box_rows);
+          }
           k_col += kBlockK;
           cur.advance(x_stages);
         }
@@ -703,7 +745,6 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
     // ----------------------------------------------------------- MMA issuers --
     const uint32_t me = warp - kFirstIssuerWarp;
     if (me < ni && lane == 0) {
-      const uint32_t idesc = ptx::idesc_bf16_f32(kBlockN, static_cast<uint32_t>(p.mma_n));
       const uint64_t xdesc0 = ptx::smem_desc_k_sw128(ptx::smem_u32(smem_x));
       const uint64_t xdesc_stage = x_stage_bytes >> 4;  // descriptor address units are 16 bytes
       const uint64_t xdesc_half = x_half_bytes >> 4;
@@ -725,6 +766,7 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
         CHORD_PROF_ADD(1, pt0);
         ptx::tc_fence_after();
         const uint32_t d_addr = tmem_base + d_col0 + (d * ni + me) * d_cols;
+        const uint32_t idesc = ptx::idesc_bf16_f32(kBlockN, static_cast<uint32_t>(t.mma_n));
         uint32_t acc = 0;
         for (int32_t kb = seg.kb; kb < seg.ke; ++kb, ++it) {
           if ((it & (ni - 1)) == me) {
@@ -956,7 +998,7 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
       const uint32_t d = d_bufs == 2 ? (segc & 1u) : 0u;
       const uint32_t dph = d_bufs == 2 ? ((segc >> 1) & 1u) : (segc & 1u);
       ptx::named_bar_sync(1, 128);  // previous segment's out_row readers are done
-      for (int32_t c = et; c < p.mma_n; c += 128) sh.out_row[c] = out_row_of(p, t, c);
+      for (int32_t c = et; c < t.mma_n; c += 128) sh.out_row[c] = out_row_of(p, t, c);
       if (seg.type == kSegOwner && et == 0) {
         // Wait (bounded) until every other slice of this tile has published its partial.
         const int* lock = p.locks + blockIdx.x;
@@ -985,11 +1027,11 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
       CHORD_PROF_ADD(1, pt0);
       CHORD_PROF_T(pt1);
       const uint32_t d_addr = tmem_base + ((q * 32u) << 16) + d_col0 + d * ni * d_cols;
-      __nv_bfloat16* out_col = p.out + t.n0 + et;
+      __nv_bfloat16* out_tile = p.out + t.n0 + q * 32;
       // Issuer i accumulated the stages it0 + j with (it0 + j) % ni == i; it took part
       // in this segment only if one of them falls inside it.
       const uint32_t seg_len = static_cast<uint32_t>(seg.ke - seg.kb);
-      for (int32_t c0 = 0; c0 < p.mma_n; c0 += 16) {
+      for (int32_t c0 = 0; c0 < t.mma_n; c0 += 16) {
         float acc[16];
 #pragma unroll
         for (int j = 0; j < 16; ++j) acc[j] = 0.0f;
@@ -1015,11 +1057,24 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
             for (int j = 0; j < 16; ++j) acc[j] += __ldcg(src + j * kBlockN);
           }
         }
+        // Transpose through shared memory so that global stores are 16 bytes wide: the
+        // warp holds 32 weight rows x 16 tokens (one token per register); staged as
+        // [token][row], each lane then stores two 8-row pieces of a token's 64 bytes.
+        __nv_bfloat16* stage = &sh.stage[q][0][0];
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          const int32_t row = sh.out_row[c0 + j];
-          if (row >= 0) out_col[static_cast<size_t>(row) * p.n] = __float2bfloat16_rn(acc[j]);
+        for (int j = 0; j < 16; ++j) stage[j * 32 + lane] = __float2bfloat16_rn(acc[j]);
+        __syncwarp();
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+          const uint32_t idx = lane + 32 * i;
+          const uint32_t tj = idx >> 2, piece = idx & 3;
+          const int32_t row = sh.out_row[c0 + tj];
+          const uint4 v = *reinterpret_cast<const uint4*>(stage + tj * 32 + piece * 8);
+          if (row >= 0) {
+            *reinterpret_cast<uint4*>(out_tile + static_cast<size_t>(row) * p.n + piece * 8) = v;
+          }
         }
+        __syncwarp();
       }
       // Release the accumulator buffer to the MMA issuer.
       ptx::tc_fence_before();

@@ -159,7 +159,7 @@ def w4a16_contiguous(
         _check_outputs(outputs, (m, weight.n), device)
     lib = _lib.load()
     with torch.cuda.device(device):
-        locks, workspace, ws_bytes = gemm_scratch(device, 128, None)
+        locks, workspace, ws_bytes = gemm_scratch(device, 256, None)
         _lib.check(lib.chord_b200_contiguous(
             inputs.data_ptr(), weight.packed.data_ptr(), weight.scale.data_ptr(),
             m_indices.data_ptr(), outputs.data_ptr(), locks.data_ptr(), locks.numel(),
