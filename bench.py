@@ -406,10 +406,10 @@ def main():
 
     with ClockSampler(local_rank) as sampler:
         ms = time_region(workload.step, args.steps, args.warmup, world, device)
+        kernel_us = time_kernels(workload, max(args.steps, 5))
+        e2e_ms = time_region(lambda: (workload.step_e2e(), torch.cuda.synchronize()), args.steps,
+                             args.warmup, world, device)
     clocks = sampler.summary()
-    kernel_us = time_kernels(workload, max(args.steps, 5))
-    e2e_ms = time_region(lambda: (workload.step_e2e(), torch.cuda.synchronize()), args.steps,
-                         args.warmup, world, device)
     assert int(status_word(device).item()) == 0, "a kernel gave up on a bounded wait"
 
     batches = {}
