@@ -109,7 +109,7 @@ class DecodeWorkload:
 
         self.device, self.batch, self.w13, self.w2 = device, batch, w13, w2
         self.topk = decode_routing(batch, seed)
-        self.block_m = chord_b200.indexed_block_m(w13, batch, TOP_K)
+        self.block_m = chord_b200.indexed_block_m(w13, batch, TOP_K, total_experts=EXPERTS_TOTAL)
         topk_dev = self.topk.to(device)
         self.sorted_ids, self.expert_ids, self.padded = fused_ops.moe_align_block_size(
             topk_dev, self.block_m, LOCAL_EXPERTS, expert_base=0)

@@ -6,6 +6,7 @@
 
 #include "../../include/chord_b200.h"
 #include "common.h"
+#include "w4a16_decode.cuh"
 #include "w4a16_gemm.cuh"
 
 namespace chord {
@@ -152,6 +153,62 @@ int launch_with_groups(const CUtensorMap& tm_w, const CUtensorMap& tm_s, const C
   return kOk;
 }
 
+// Token tiles of at most 32 rows (indexed, masked) have a kernel of their own, in which
+// every warpgroup of a CTA is an independent worker with a lock word and a scratch
+// slot of its own: four times as many of each as the general kernel needs.
+bool decode_kernel_applies(const GemmParams& p) {
+  return options().decode_kernel != 0 && p.mode != kModeContiguous && p.mma_n <= kDecMaxTokens;
+}
+
+int decode_workers(int grid) { return grid * kDecWorkers; }
+
+int64_t decode_workspace_bytes(int grid, int mma_n) {
+  return static_cast<int64_t>(decode_workers(grid)) * kBlockN * mma_n * 4;
+}
+
+int launch_decode(GemmParams p, const DeviceInfo& dev, const int32_t* packed, const void* scale,
+                  int grid, cudaStream_t stream) {
+  // Shared memory: one ring per worker, as deep as fits next to the barriers and the
+  // epilogue buffers.  Two stages are being read by MMAs in flight and two more wait
+  // for their activation gather to be published, so fewer than six would stall.
+  const size_t fixed = sizeof(DecodeShared) + 1024;
+  const size_t stage_bytes = decode_stage_bytes(p.mma_n);
+  int stages = static_cast<int>((static_cast<size_t>(dev.max_smem_optin) - fixed) / kDecWorkers / stage_bytes);
+  if (stages > kDecMaxStages) stages = kDecMaxStages;
+  const int cap = options().max_stages;
+  if (cap > 0 && stages > cap) stages = cap < 4 ? 4 : cap;
+  CHORD_REQUIRE(stages >= 4, "internal: decode ring too shallow (%d stages)", stages);
+  p.w_stages = stages;
+  p.x_stages = stages;
+  CUtensorMap tm_w, tm_s;
+  if (int rc = make_map_2d(&tm_w, packed, CU_TENSOR_MAP_DATA_TYPE_INT32, 4,
+                           static_cast<uint64_t>(p.n) * 2,
+                           static_cast<uint64_t>(p.num_experts) * (p.k / 16), 256, kDecStepK / 16,
+                           CU_TENSOR_MAP_SWIZZLE_NONE))
+    return rc;
+  if (int rc = make_map_2d(&tm_s, scale, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+                           static_cast<uint64_t>(p.n),
+                           static_cast<uint64_t>(p.num_experts) * (p.k / 32), kBlockN,
+                           kDecStepK / 32, CU_TENSOR_MAP_SWIZZLE_NONE))
+    return rc;
+  const size_t smem = kDecWorkers * static_cast<size_t>(stages) * stage_bytes + fixed;
+  static std::once_flag flags[64];
+  static cudaError_t attr_result[64];
+  int device = 0;
+  CHORD_CUDA(cudaGetDevice(&device));
+  std::call_once(flags[device & 63], [&] {
+    attr_result[device & 63] = cudaFuncSetAttribute(
+        w4a16_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, dev.max_smem_optin);
+  });
+  if (attr_result[device & 63] != cudaSuccess) {
+    return fail(kCudaError, "cudaFuncSetAttribute failed: %s",
+                cudaGetErrorString(attr_result[device & 63]));
+  }
+  w4a16_decode_kernel<<<grid, kDecThreads, smem, stream>>>(tm_w, tm_s, p);
+  CHORD_CUDA(cudaGetLastError());
+  return kOk;
+}
+
 // Common tail of the three operators: weight/scale/activation descriptors,
 // pipeline depth, scratch checks, launch.
 int launch_gemm(GemmParams p, const void* x, const int32_t* packed, const void* scale,
@@ -176,6 +233,15 @@ int launch_gemm(GemmParams p, const void* x, const int32_t* packed, const void* 
                 "activation tensor too large for 32-bit element offsets");
   const int grid = grid_size(dev);
   p.mma_n = round_up16(p.tile_tokens);
+  p.profile = reinterpret_cast<unsigned long long*>(options().profile_buffer);
+  p.ablate = options().ablate;
+  // The decode kernel runs when the caller's locks and scratch are large enough for
+  // one per warpgroup; with the smaller buffers of the general kernel, that one runs.
+  if (decode_kernel_applies(p) && p.locks != nullptr && p.workspace != nullptr &&
+      num_locks >= decode_workers(grid) && workspace_bytes >= decode_workspace_bytes(grid, p.mma_n)) {
+    p.num_locks = static_cast<int32_t>(num_locks);
+    return launch_decode(p, dev, packed, scale, grid, static_cast<cudaStream_t>(stream));
+  }
   p.x_stages = pick_x_stages(p.mma_n);
   p.w_stages = pick_w_stages(dev, p.mma_n, p.x_stages);
   CHORD_REQUIRE(p.w_stages >= 2, "token tile %d leaves room for fewer than two pipeline stages",
@@ -207,8 +273,6 @@ int launch_gemm(GemmParams p, const void* x, const int32_t* packed, const void* 
                 p.a_stages, p.w_stages, p.x_stages, groups, p.issuers);
   p.x_load = p.mode == kModeIndexed ? (options().x_load == 1 ? kXLoadGather4 : kXLoadCpAsync)
                                     : kXLoadTiled;
-  p.profile = reinterpret_cast<unsigned long long*>(options().profile_buffer);
-  p.ablate = options().ablate;
   p.num_locks = static_cast<int32_t>(num_locks);
   CHORD_REQUIRE(p.locks != nullptr && num_locks >= grid,
                 "stream-K needs a zeroed locks buffer of at least %d lock words, got %lld", grid,
@@ -308,14 +372,16 @@ int64_t chord_b200_gemm_workspace_bytes(int64_t tile_tokens) {
                 static_cast<long long>(tile_tokens), chord::kMaxTileTokens);
     return -1;
   }
-  return static_cast<int64_t>(chord::grid_size(dev)) * chord::kBlockN *
-         chord::round_up16(tile_tokens) * 4;
+  const int grid = chord::grid_size(dev);
+  const int mma_n = chord::round_up16(tile_tokens);
+  if (mma_n <= chord::kDecMaxTokens) return chord::decode_workspace_bytes(grid, mma_n);
+  return static_cast<int64_t>(grid) * chord::kBlockN * mma_n * 4;
 }
 
 int chord_b200_gemm_lock_words(void) {
   chord::DeviceInfo dev;
   if (chord::current_device_info(&dev)) return -1;
-  return chord::grid_size(dev);
+  return chord::decode_workers(chord::grid_size(dev));
 }
 
 int64_t chord_b200_schedule_segments(int64_t tiles, int64_t k, int64_t grid, int64_t cta,

@@ -170,6 +170,15 @@ __device__ __forceinline__ void tma_gather4(uint32_t dst, const void* tmap, uint
 constexpr uint64_t kEvictFirst = 0x12F0000000000000ull;
 constexpr uint64_t kEvictLast = 0x14F0000000000000ull;
 
+// 8-byte shared-memory load from a 32-bit shared address plus a compile-time offset
+// (the offset folds into the instruction, so unrolled loads share one address register).
+template <int kOffset>
+__device__ __forceinline__ uint2 lds64(uint32_t addr) {
+  uint2 v;
+  asm volatile("ld.shared.v2.u32 {%0, %1}, [%2+%3];" : "=r"(v.x), "=r"(v.y) : "r"(addr), "n"(kOffset) : "memory");
+  return v;
+}
+
 // ------------------------------------------------------------ cp.async (LSU) --
 
 __device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src, bool valid) {
@@ -351,6 +360,14 @@ __device__ __forceinline__ int ld_acquire(const int* addr) {
   int v;
   asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(addr) : "memory");
   return v;
+}
+
+// Shared-memory counter increment that orders the caller's earlier writes before it
+// and later reads after it (CTA scope); returns the previous value.
+__device__ __forceinline__ uint32_t atom_add_acq_rel_shared(uint32_t addr, uint32_t v) {
+  uint32_t old;
+  asm volatile("atom.acq_rel.cta.shared::cta.add.u32 %0, [%1], %2;" : "=r"(old) : "r"(addr), "r"(v) : "memory");
+  return old;
 }
 
 __device__ __forceinline__ void named_bar_sync(uint32_t id, uint32_t nthreads) {

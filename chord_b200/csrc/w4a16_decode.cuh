@@ -1,0 +1,583 @@
+// Decode-sized variant of the W4A16 grouped GEMM (token tiles of at most 32 rows).
+//
+// Same data formats, numerics, scheduling and stream-K protocol as
+// w4a16_gemm_kernel (w4a16_gemm.cuh); what changes is who does what.  With a
+// handful of tokens per tile the MMAs are tiny and the kernel is bound by the number
+// of instructions it spends per weight byte (the integer pipe that pulls the nibbles
+// apart runs at half rate), so every barrier round trip between specialised warps and
+// every address computation counts.  Here each of the four warpgroups of a CTA is a
+// self-contained worker with a feeder warp and an MMA issuer warp of its own:
+//
+//   * it has its own slice of the work (the grid of workers is 4 x the grid of CTAs),
+//     its own shared-memory ring and its own 128 tensor-memory columns
+//     (three 32-column operand slots + up to 32 accumulator columns);
+//   * a ring stage holds everything one 64-wide K step needs: 4 KB of packed weights
+//     and 512 B of scales (two TMA boxes) and the step's activation rows
+//     (cp.async gather, 128-byte swizzle).  The worker's feeder warp fills it:
+//     lane 0 issues the TMA, all 32 lanes gather the activation rows.  The weight half
+//     of a stage is handed back as soon as the warps have read it, so the HBM stream
+//     runs a full ring ahead; the activation half waits for the MMAs that read it;
+//   * per step each of the worker's four warps reads its packed words, dequantises
+//     them and stores them to one of three operand slots in tensor memory; the
+//     worker's issuer warp then issues the step's four tcgen05.mma, whose completion
+//     frees the activation half of the stage and the operand slot.  The four warps do
+//     not wait for one another inside a tile;
+//   * after the last step of a tile the same four warps run the epilogue.
+#pragma once
+
+#include "w4a16_gemm.cuh"
+
+#ifndef DEC_ABLATE
+#define DEC_ABLATE 0
+#endif
+
+namespace chord {
+
+constexpr int kDecStepK = 64;                        // K elements per step
+constexpr int kDecWBytes = (kDecStepK / 16) * 1024;  // packed weights per step
+constexpr int kDecSBytes = (kDecStepK / 32) * 256;   // scales per step
+constexpr int kDecWSBytes = 5120;                    // weights + scales, padded to keep stages 1024-aligned
+constexpr int kDecMaxStages = 12;
+constexpr int kDecMaxTokens = 32;
+constexpr int kDecWorkers = 4;                       // warpgroups per CTA
+constexpr int kDecThreads = 32 * (2 * kDecWorkers + 4 * kDecWorkers);  // feeders, issuers, workers
+constexpr int kDecSlots = 3;                         // operand slots (32 TMEM columns each) per worker
+constexpr int kDecDCol = 32 * kDecSlots;             // the worker's accumulator follows its operand slots
+
+struct __align__(16) DecodeWorkerShared {
+  uint64_t wfull[kDecMaxStages];   // weights and scales landed (1 arrival + TMA bytes)
+  uint64_t wempty[kDecMaxStages];  // the four warps have them in registers (4 arrivals)
+  uint64_t xfull[kDecMaxStages];   // activation rows landed and visible to the tensor core (1 arrival)
+  uint64_t xempty[kDecMaxStages];  // the MMAs reading them have completed (1 commit)
+  uint64_t afree[kDecSlots];      // the MMAs reading the operand slot have completed (1 commit)
+  uint64_t afull[kDecSlots];      // operand slot stored by the four warps (4 arrivals)
+  int32_t out_row[kDecMaxTokens];
+  __align__(16) __nv_bfloat16 stage[4][16][32];  // epilogue transpose buffers, one per warp
+};
+
+struct __align__(16) DecodeShared {
+  DecodeWorkerShared worker[kDecWorkers];
+  uint32_t tmem_base;
+  uint32_t abort_flag;
+  int32_t m_blocks;
+  int32_t pad;
+  int32_t group_prefix[kMaxGroups + 1];  // masked: first M tile of each group
+};
+
+__device__ __forceinline__ bool z_keep(uint32_t a, uint32_t b) { return a == 0x13572468u && b == 0x24681357u; }
+
+// Bytes of one ring stage: activation rows first (1024-aligned for the swizzle).
+__host__ __device__ inline uint32_t decode_stage_bytes(int mma_n) {
+  return static_cast<uint32_t>(mma_n) * 128u + kDecWSBytes;
+}
+
+// decode_tile() of the general kernel without its contiguous branch (not served here),
+// plus the tile's own MMA N: 16 when no token slot beyond the sixteenth carries a row,
+// which is the common case at decode sizes whatever block size the routing was
+// aligned to.  A tile without any row is not valid (nothing to compute).  Must be
+// called by all 32 lanes of a warp.
+__device__ __forceinline__ TileInfo decode_tile_small(const GemmParams& p, const int32_t* group_prefix,
+                                                      int32_t tile) {
+  TileInfo t;
+  const int32_t n_blocks = p.n / kBlockN;
+  const int32_t mb = tile / n_blocks;
+  t.n0 = (tile - mb * n_blocks) * kBlockN;
+  t.m0 = 0;
+  t.limit = 0;
+  t.mma_n = p.mma_n;
+  if (p.mode == kModeIndexed) {
+    t.expert = __ldg(p.expert_ids + mb);
+    t.ntok = p.tile_tokens;
+    t.base = mb * p.tile_tokens;
+    const int32_t lane = static_cast<int32_t>(threadIdx.x & 31u);
+    const int32_t id = lane < p.tile_tokens ? __ldg(p.sorted_ids + t.base + lane) : -1;
+    const uint32_t rows = __ballot_sync(0xffffffffu, id >= 0 && id < p.out_rows && id / p.top_k < p.x_rows);
+    t.ntok = 32 - __clz(static_cast<int32_t>(rows));  // one past the last slot that carries a row
+    t.mma_n = t.ntok <= 16 ? 16 : 32;
+  } else {
+    int32_t lo = 0, hi = p.num_experts;
+    while (hi - lo > 1) {
+      const int32_t mid = (lo + hi) >> 1;
+      if (group_prefix[mid] <= mb) lo = mid; else hi = mid;
+    }
+    t.expert = lo;
+    t.m0 = (mb - group_prefix[lo]) * p.tile_tokens;
+    int32_t mm = __ldg(p.masked_m + lo);
+    mm = mm < 0 ? 0 : (mm > p.max_m ? p.max_m : mm);
+    t.limit = mm;
+    const int32_t left = mm - t.m0;
+    t.ntok = left < p.tile_tokens ? left : p.tile_tokens;
+    t.base = lo * p.max_m;
+    t.mma_n = t.ntok <= 16 ? 16 : 32;
+  }
+  t.valid = t.expert >= 0 && t.expert < p.num_experts && t.ntok > 0;
+  return t;
+}
+
+// The steps (tile, 64-wide K block) of one worker in order, one at a time.
+struct StepStream {
+  SegmentIterator iter;
+  Segment seg;
+  TileInfo t;
+  int32_t kb;
+  bool live;
+
+  __device__ void init(int32_t tiles, int32_t k_steps, int32_t workers, int32_t worker) {
+    iter.init(tiles, k_steps, workers, worker);
+    live = false;
+    kb = 0;
+  }
+
+  // Moves to the next step; `first` tells whether it opens a new segment.
+  __device__ bool next(const GemmParams& p, const int32_t* group_prefix, bool& first) {
+    if (live && ++kb < seg.ke) {
+      first = false;
+      return true;
+    }
+    while (iter.next(seg)) {
+      t = decode_tile_small(p, group_prefix, seg.tile);
+      if (!t.valid) continue;
+      kb = seg.kb;
+      live = true;
+      first = true;
+      return true;
+    }
+    live = false;
+    return false;
+  }
+};
+
+__global__ void __launch_bounds__(kDecThreads, 1)
+w4a16_decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_s,
+                    const GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  // Dynamic shared memory, 1024-aligned: one ring per worker, then DecodeShared.
+  const uint32_t raw_addr = ptx::smem_u32(smem_raw);
+  uint8_t* smem = smem_raw + ((1024u - (raw_addr & 1023u)) & 1023u);
+  const uint32_t stages = static_cast<uint32_t>(p.w_stages);
+  const uint32_t x_bytes = static_cast<uint32_t>(p.mma_n) * 128u;
+  const uint32_t stage_bytes = x_bytes + kDecWSBytes;
+  const uint32_t worker_bytes = stages * stage_bytes;
+  DecodeShared& sh = *reinterpret_cast<DecodeShared*>(smem + kDecWorkers * worker_bytes);
+
+  const uint32_t warp = threadIdx.x >> 5;
+  const uint32_t lane = threadIdx.x & 31;
+  const int32_t k_steps = p.k / kDecStepK;
+
+  if (threadIdx.x == 0) {
+    ptx::prefetch_tensormap(&tm_w);
+    ptx::prefetch_tensormap(&tm_s);
+    for (int w = 0; w < kDecWorkers; ++w) {
+      for (uint32_t s = 0; s < stages; ++s) {
+        ptx::mbar_init(ptx::smem_u32(&sh.worker[w].wfull[s]), 1);
+        ptx::mbar_init(ptx::smem_u32(&sh.worker[w].wempty[s]), 4);
+        ptx::mbar_init(ptx::smem_u32(&sh.worker[w].xfull[s]), 1);
+        ptx::mbar_init(ptx::smem_u32(&sh.worker[w].xempty[s]), 1);
+      }
+      for (int j = 0; j < kDecSlots; ++j) {
+        ptx::mbar_init(ptx::smem_u32(&sh.worker[w].afull[j]), 4);
+        ptx::mbar_init(ptx::smem_u32(&sh.worker[w].afree[j]), 1);
+      }
+    }
+    sh.abort_flag = 0;
+    ptx::fence_barrier_init();
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc(ptx::smem_u32(&sh.tmem_base), kTmemCols);
+    ptx::tmem_relinquish();
+  }
+  // Activation rows no gather ever fills must not hold NaN patterns.
+  {
+    uint4* ring_words = reinterpret_cast<uint4*>(smem);
+    for (uint32_t i = threadIdx.x; i < kDecWorkers * worker_bytes / 16; i += blockDim.x) {
+      ring_words[i] = make_uint4(0, 0, 0, 0);
+    }
+  }
+  if (threadIdx.x == 0) {
+    if (p.mode == kModeMasked) {
+      int32_t acc = 0;
+      for (int32_t g = 0; g < p.num_experts; ++g) {
+        sh.group_prefix[g] = acc;
+        int32_t mm = __ldg(p.masked_m + g);
+        mm = mm < 0 ? 0 : (mm > p.max_m ? p.max_m : mm);
+        acc += (mm + p.tile_tokens - 1) / p.tile_tokens;
+      }
+      sh.group_prefix[p.num_experts] = acc;
+      sh.m_blocks = acc;
+    } else {
+      int32_t padded = __ldg(p.num_tokens_padded);
+      padded = padded < 0 ? 0 : (padded > p.sorted_len ? p.sorted_len : padded);
+      const int32_t blocks = padded / p.tile_tokens;
+      sh.m_blocks = blocks > p.expert_len ? p.expert_len : blocks;
+    }
+  }
+  ptx::fence_proxy_async();
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::tc_fence_after();
+
+  const uint32_t tmem_base = sh.tmem_base;
+  volatile uint32_t* abort_flag = &sh.abort_flag;
+  const int32_t tiles = sh.m_blocks * (p.n / kBlockN);
+  // warps 0-3 feed, warps 4-7 issue the MMAs, warps 8-23 are the four workers
+  const uint32_t wk = warp < 8 ? (warp & 3u) : (warp - 8) >> 2;
+  const int32_t worker_id = static_cast<int32_t>(blockIdx.x) * kDecWorkers + static_cast<int32_t>(wk);
+  SegmentIterator iter;
+  iter.init(tiles, k_steps, static_cast<int32_t>(gridDim.x) * kDecWorkers, worker_id);
+  Segment seg;
+  DecodeWorkerShared& ws = sh.worker[wk];
+  const uint32_t ring = ptx::smem_u32(smem + wk * worker_bytes);  // shared address of stage 0
+  const uint32_t wfull0 = ptx::smem_u32(&ws.wfull[0]);
+  const uint32_t wempty0 = ptx::smem_u32(&ws.wempty[0]);
+  const uint32_t xfull0 = ptx::smem_u32(&ws.xfull[0]);
+  const uint32_t xempty0 = ptx::smem_u32(&ws.xempty[0]);
+  const uint32_t afree0 = ptx::smem_u32(&ws.afree[0]);
+  const uint32_t afull0 = ptx::smem_u32(&ws.afull[0]);
+  const uint32_t col0 = wk * 128u;  // this worker's tensor-memory columns
+
+  if (warp < 4) {
+    // ------------------------- feeder of worker `warp`: weights, scales, activations --
+    // The two halves of a stage have different lifetimes: the packed weights and scales
+    // are free again as soon as the worker's warps hold them in registers, the
+    // activation rows only when the MMAs that read them have completed.  The feeder
+    // therefore walks the worker's step sequence twice: `wsm` (lane 0: two TMA boxes per
+    // step) runs stages - 2 steps ahead of `xsm` (all lanes: cp.async gather, lane l
+    // fetching the 16-byte piece l % 8 of rows l / 8 + 4 b, b < mma_n / 4).  In steady
+    // state both waits below are over when they are reached, and the weight stream stays
+    // a full ring ahead of the workers.
+    const uint32_t piece = lane & 7u;
+    const uint32_t r0 = lane >> 3;
+    uint32_t dst_off[2];
+#pragma unroll
+    for (int b = 0; b < 2; ++b) {
+      const uint32_t r = r0 + 4u * b;
+      dst_off[b] = r * 128u + ((piece ^ (r & 7u)) << 4);
+    }
+    StepStream wsm, xsm;
+    wsm.init(tiles, k_steps, static_cast<int32_t>(gridDim.x) * kDecWorkers, worker_id);
+    xsm = wsm;
+    StageCursor wcur, xcur, xdone;
+    bool x_pending = false;
+    const int32_t w_lead = static_cast<int32_t>(stages) - 2;
+    int32_t w_ahead = 0;
+    bool w_more = true, ok = true;
+    int32_t w_row = 0, s_row = 0, w_col = 0;
+    int32_t x_off[8];
+    uint32_t active = 0;  // bit b: some lane has a row to fetch in round b
+    const __nv_bfloat16* src = p.x;
+    CHORD_PROF_INIT();
+    while (ok) {
+      while (w_more && w_ahead <= w_lead) {
+        bool first = false;
+        if (!wsm.next(p, sh.group_prefix, first)) {
+          w_more = false;
+          break;
+        }
+        if (first) {
+          w_row = wsm.t.expert * (p.k / 16) + wsm.kb * (kDecStepK / 16);
+          s_row = wsm.t.expert * (p.k / 32) + wsm.kb * (kDecStepK / 32);
+          w_col = wsm.t.n0;
+        }
+        CHORD_PROF_T(ft0);
+        if (!ptx::mbar_wait_warp(wempty0 + wcur.s * 8u, wcur.ph ^ 1u, abort_flag)) {
+          ok = false;
+          break;
+        }
+        CHORD_PROF_ADD(1, ft0);
+        CHORD_PROF_T(ft1);
+        if (lane == 0) {
+          const uint32_t st = ring + wcur.s * stage_bytes + x_bytes;
+          const uint32_t full = wfull0 + wcur.s * 8u;
+          ptx::mbar_arrive_expect_tx(full, kDecWBytes + kDecSBytes);
+          ptx::tma_load_2d(st, &tm_w, full, 2 * w_col, w_row);
+          ptx::tma_load_2d(st + kDecWBytes, &tm_s, full, w_col, s_row);
+        }
+        __syncwarp();
+        CHORD_PROF_ADD(2, ft1);
+        w_row += kDecStepK / 16;
+        s_row += kDecStepK / 32;
+        wcur.advance(stages);
+        ++w_ahead;
+      }
+      if (!ok) break;
+      bool first = false;
+      if (!xsm.next(p, sh.group_prefix, first)) break;
+      if (first) {
+        active = 0;
+#pragma unroll
+        for (int b = 0; b < 8; ++b) {
+          const int32_t slot = static_cast<int32_t>(r0) + 4 * b;
+          int32_t off = -1;
+          if (slot < xsm.t.ntok) {
+            const int32_t row = x_row_of(p, xsm.t, slot);
+            if (row < p.x_rows) off = row * p.k;
+          }
+          x_off[b] = off;
+          if (__ballot_sync(0xffffffffu, off >= 0) != 0) active |= 1u << b;
+        }
+        src = p.x + xsm.kb * kDecStepK + piece * 8;
+      }
+      CHORD_PROF_T(ft2);
+      if (!ptx::mbar_wait_warp(xempty0 + xcur.s * 8u, xcur.ph ^ 1u, abort_flag)) {
+        ok = false;
+        break;
+      }
+      CHORD_PROF_ADD(3, ft2);
+      CHORD_PROF_T(ft3);
+      const uint32_t xs = ring + xcur.s * stage_bytes;
+#pragma unroll
+      for (int b = 0; b < 8; ++b) {
+        if (!(DEC_ABLATE & 8) && ((active >> b) & 1u) && x_off[b] >= 0) {
+          ptx::cp_async_16(xs + dst_off[b & 1] + (b >> 1) * 1024u, src + x_off[b], true);
+        }
+      }
+      ptx::cp_async_commit();
+      // The previous step's rows have landed by now: make them visible to the tensor
+      // core (they were written through the generic proxy) and publish them.
+      if (x_pending) {
+        ptx::cp_async_wait_group<1>();
+        ptx::fence_proxy_async();
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(xfull0 + xdone.s * 8u);
+        xdone.advance(stages);
+      }
+      x_pending = true;
+      src += kDecStepK;
+      xcur.advance(stages);
+      --w_ahead;
+      CHORD_PROF_ADD(4, ft3);
+    }
+    // Publish the last step (also when leaving on a timeout: nothing may stay in
+    // flight towards shared memory when the CTA retires).
+    ptx::cp_async_wait_all();
+    ptx::fence_proxy_async();
+    __syncwarp();
+    if (x_pending && lane == 0) ptx::mbar_arrive(xfull0 + xdone.s * 8u);
+    if (wk == 0) CHORD_PROF_FLUSH(2);
+    if (!ok && lane == 0) {
+      sh.abort_flag = 1;
+      if (p.status) atomicOr(p.status, kStatusProducerTimeout);
+    }
+    __syncwarp();
+  } else if (warp < 8) {
+    // ------------------------------------------------- MMA issuer of worker `warp - 4` --
+    // One tcgen05.mma costs its issuing thread some tens of cycles whatever its size, and
+    // a 64-wide step needs four: kept off the warps that dequantise.
+    const uint32_t d_tm = tmem_base + col0 + kDecDCol;
+    StageCursor cur, slot;
+    bool ok = true;
+    while (ok && iter.next(seg)) {
+      const TileInfo t = decode_tile_small(p, sh.group_prefix, seg.tile);
+      if (!t.valid) continue;
+      const uint32_t idesc = ptx::idesc_bf16_f32(kBlockN, static_cast<uint32_t>(t.mma_n));
+      uint32_t acc = 0;
+      for (int32_t kb = seg.kb; kb < seg.ke; ++kb) {
+        // No wait is needed for the accumulator: the first store of a segment follows
+        // its warp's share of the previous segment's epilogue.
+        if (!ptx::mbar_wait_warp(afull0 + slot.s * 8u, slot.ph, abort_flag) ||
+            !ptx::mbar_wait_warp(xfull0 + cur.s * 8u, cur.ph, abort_flag)) {
+          ok = false;
+          break;
+        }
+        ptx::tc_fence_after();
+        if (lane == 0) {
+          const uint64_t xdesc = ptx::smem_desc_k_sw128(ring + cur.s * stage_bytes);
+          const uint32_t a_tm = tmem_base + col0 + slot.s * 32u;
+          if (!(DEC_ABLATE & 1)) {
+            ptx::mma_ts(d_tm, a_tm, xdesc, idesc, acc);
+            ptx::mma_ts(d_tm, a_tm + 8, xdesc + 2, idesc, 1);
+            ptx::mma_ts(d_tm, a_tm + 16, xdesc + 4, idesc, 1);
+            ptx::mma_ts(d_tm, a_tm + 24, xdesc + 6, idesc, 1);
+          }
+          ptx::mma_commit(xempty0 + cur.s * 8u);
+          ptx::mma_commit(afree0 + slot.s * 8u);
+        }
+        __syncwarp();
+        acc = 1;
+        cur.advance(stages);
+        slot.advance(kDecSlots);
+      }
+    }
+    if (!ok && lane == 0) {
+      sh.abort_flag = 1;
+      if (p.status) atomicOr(p.status, kStatusMmaTimeout);
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------------------------------------- worker warps --
+    // Inside a segment the four warps run independently: each waits for the stage,
+    // dequantises its 32 weight rows, waits for a free operand slot, stores, and tells
+    // the feeder.  They meet (named barrier) only around the epilogue.  Control flow is
+    // the same in all four whatever happens: a warp whose bounded wait gave up clears
+    // `ok` and skips the work, but still walks the loops and meets its siblings at every
+    // named barrier; the abort flag it raises makes the others' waits give up quickly.
+    const uint32_t q = warp & 3;                          // TMEM lane quarter == 32 weight rows
+    const uint32_t wt = threadIdx.x - (8 + 4 * wk) * 32;  // 0..127 inside the worker
+    const uint32_t bar_id = 1 + wk;
+    // This thread's two packed words per K16 row (slabs 2(q&1), 2(q&1)+1 of the 64-row
+    // chunk q>>1) and its four scales per K32 group, as offsets into a stage.
+    const uint32_t w_off = x_bytes + (q >> 1) * 512u + lane * 16u + (q & 1) * 8u;
+    const uint32_t s_off = x_bytes + kDecWBytes + (q >> 1) * 128u + (lane >> 2) * 16u + (q & 1) * 8u;
+    const uint32_t a_lane = tmem_base + ((q * 32u) << 16) + col0;
+    StageCursor cur, slot;
+    bool ok = true;
+    CHORD_PROF_INIT();
+    const size_t ws_slot = static_cast<size_t>(kBlockN) * p.mma_n;
+
+    while (iter.next(seg)) {
+      const TileInfo t = decode_tile_small(p, sh.group_prefix, seg.tile);
+      if (!t.valid) continue;
+      const int32_t n_steps = seg.ke - seg.kb;
+      if (wt < static_cast<uint32_t>(t.mma_n)) ws.out_row[wt] = out_row_of(p, t, static_cast<int32_t>(wt));
+      uint32_t last_bar = 0, last_ph = 0;
+      for (int32_t j = 0; j < n_steps; ++j) {
+        const uint32_t st = ring + cur.s * stage_bytes;
+        CHORD_PROF_T(pt0);
+        if (ok) ok = ptx::mbar_wait_warp(wfull0 + cur.s * 8u, cur.ph, abort_flag);
+        CHORD_PROF_ADD(1, pt0);
+        if (ok) {
+          CHORD_PROF_T(pt1);
+          uint2 words[4], scales[2];
+          words[0] = ptx::lds64<0>(st + w_off);
+          words[1] = ptx::lds64<1024>(st + w_off);
+          words[2] = ptx::lds64<2048>(st + w_off);
+          words[3] = ptx::lds64<3072>(st + w_off);
+          scales[0] = ptx::lds64<0>(st + s_off);
+          scales[1] = ptx::lds64<256>(st + s_off);
+          __syncwarp();
+          if (lane == 0) ptx::mbar_arrive(wempty0 + cur.s * 8u);
+          uint32_t lo[16], hi[16];
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const uint2 sc = scales[i >> 1];
+            // sc.x = {slab A row r, slab A row r+8}; sc.y = same for slab B.
+            const uint32_t a_lo = __byte_perm(sc.x, 0, 0x1010);
+            const uint32_t a_hi = __byte_perm(sc.x, 0, 0x3232);
+            const uint32_t b_lo = __byte_perm(sc.y, 0, 0x1010);
+            const uint32_t b_hi = __byte_perm(sc.y, 0, 0x3232);
+            if (DEC_ABLATE & 2) {
+#pragma unroll
+              for (int z = 0; z < 4; ++z) {
+                lo[4 * i + z] = words[i].x ^ a_lo;
+                hi[4 * i + z] = words[i].y ^ b_hi;
+              }
+              if (z_keep(a_hi, b_lo)) sh.pad = 1;
+            } else {
+              dequant_word(words[i].x, a_lo, a_hi, lo + 4 * i);
+              dequant_word(words[i].y, b_lo, b_hi, hi + 4 * i);
+            }
+          }
+          CHORD_PROF_ADD(2, pt1);
+          // The operand slot is free once the MMAs of its previous use have completed.
+          CHORD_PROF_T(pt2);
+          const uint32_t afree = afree0 + slot.s * 8u;
+          ok = ptx::mbar_wait_warp(afree, slot.ph ^ 1u, abort_flag);
+          CHORD_PROF_ADD(3, pt2);
+          if (ok) {
+            CHORD_PROF_T(pt3);
+            ptx::tc_fence_after();
+            const uint32_t a_addr = a_lane + slot.s * 32u;
+            ptx::tmem_st_16x128b_x8(a_addr, lo);
+            ptx::tmem_st_16x128b_x8(a_addr + (16u << 16), hi);
+            ptx::tmem_wait_st();
+            ptx::tc_fence_before();
+            __syncwarp();
+            CHORD_PROF_ADD(4, pt3);
+            CHORD_PROF_T(pt4);
+            if (lane == 0) ptx::mbar_arrive(afull0 + slot.s * 8u);
+            __syncwarp();
+            CHORD_PROF_ADD(5, pt4);
+          }
+          last_bar = afree;
+          last_ph = slot.ph;
+        }
+        if (!ok) sh.abort_flag = 1;
+        cur.advance(stages);
+        slot.advance(kDecSlots);
+      }
+      // ---- end of the segment: wait for its last MMAs, then drain the accumulator.
+      {
+        if (ok) ok = ptx::mbar_wait_warp(last_bar, last_ph, abort_flag);
+        ptx::tc_fence_after();
+        if (ok && seg.type == kSegOwner && wt == 0) {
+          const int* lock = p.locks + worker_id;
+          bool lock_ok = false;
+          for (uint32_t spin = 0; spin < (1u << 22); ++spin) {
+            if (ptx::ld_acquire(lock) >= seg.peer) {
+              lock_ok = true;
+              break;
+            }
+            __nanosleep(64);
+          }
+          if (!lock_ok && p.status) atomicOr(p.status, kStatusLockTimeout);
+        }
+        ptx::named_bar_sync(bar_id, 128);  // out_row written, lock observed
+        if (ok) {
+          const uint32_t d_addr = tmem_base + ((q * 32u) << 16) + col0 + kDecDCol;
+          __nv_bfloat16* out_tile = p.out + t.n0 + q * 32;
+          for (int32_t c0 = 0; c0 < t.mma_n; c0 += 16) {
+            uint32_t v[16];
+            ptx::tmem_ld_32x32b_x16(d_addr + c0, v);
+            ptx::tmem_wait_ld();
+            float accv[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) accv[i] = __uint_as_float(v[i]);
+            if (seg.type == kSegContrib) {
+              float* dst = p.workspace + worker_id * ws_slot + static_cast<size_t>(c0) * kBlockN + q * 32 + lane;
+#pragma unroll
+              for (int i = 0; i < 16; ++i) __stcg(dst + i * kBlockN, accv[i]);
+              continue;
+            }
+            if (seg.type == kSegOwner) {
+              for (int32_t peer = 1; peer <= seg.peer; ++peer) {
+                const float* part = p.workspace + (worker_id + peer) * ws_slot +
+                                    static_cast<size_t>(c0) * kBlockN + q * 32 + lane;
+#pragma unroll
+                for (int i = 0; i < 16; ++i) accv[i] += __ldcg(part + i * kBlockN);
+              }
+            }
+            // Transpose through shared memory so that global stores are 16 bytes wide.
+            __nv_bfloat16* stage = &ws.stage[q][0][0];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) stage[i * 32 + lane] = __float2bfloat16_rn(accv[i]);
+            __syncwarp();
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+              const uint32_t idx = lane + 32 * i;
+              const uint32_t tj = idx >> 2, pc = idx & 3;
+              const int32_t row = ws.out_row[c0 + tj];
+              const uint4 val = *reinterpret_cast<const uint4*>(stage + tj * 32 + pc * 8);
+              if (row >= 0) {
+                *reinterpret_cast<uint4*>(out_tile + static_cast<size_t>(row) * p.n + pc * 8) = val;
+              }
+            }
+            __syncwarp();
+          }
+          ptx::tc_fence_before();
+          if (seg.type == kSegContrib) __threadfence();
+        }
+        ptx::named_bar_sync(bar_id, 128);  // accumulator and out_row are free again
+        if (wt == 0) {
+          // The stream-K handshake is completed even after a failure, so that no other
+          // worker spins on a lock that would never move; the status word tells the host.
+          if (seg.type == kSegContrib) ptx::red_release_add(p.locks + seg.peer, 1);
+          else if (seg.type == kSegOwner) p.locks[worker_id] = 0;
+        }
+      }
+    }
+    if (wk == 0 && q < 2) CHORD_PROF_FLUSH(q);
+    if (!ok && lane == 0) {
+      sh.abort_flag = 1;
+      if (p.status) atomicOr(p.status, kStatusDequantTimeout);
+    }
+  }
+
+  ptx::tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    ptx::tc_fence_after();
+    ptx::tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+}  // namespace chord

@@ -140,16 +140,29 @@ def select_block_m(shape_n: int, shape_k: int, num_experts: int, routed_m: int) 
     return int(_lib.load().chord_b200_indexed_block_m(shape_n, shape_k, num_experts, routed_m))
 
 
-def indexed_block_m(weight: PreparedWeight, num_tokens: int, top_k: int, *, device=None) -> int:
+def indexed_block_m(weight: PreparedWeight, num_tokens: int, top_k: int, *, device=None,
+                    total_experts: int | None = None) -> int:
     """Routing block size ``indexed`` uses; align ``moe_align_block_size`` to it.
 
     For down pass gate/up's ``top_k`` here (the kernel call takes ``top_k=1``).
-    Same signature as chord_kernels/operator/api.py:300-315.
+    Same signature as chord_kernels/operator/api.py:300-315, plus one optional
+    keyword: under expert parallelism ``weight`` holds only this rank's experts while
+    the router spreads ``num_tokens * top_k`` routes over ``total_experts``; naming the
+    total lets the block size follow the rows this rank will really see (the
+    reference folds that knowledge into per-deployment tuning tables,
+    chord_kernels/operator/tuning.py:496-504).
     """
     if not isinstance(weight, PreparedWeight):
         raise TypeError("weight must be a PreparedWeight from pack_w4a16()")
     del device  # one schedule family: the block size does not depend on the GPU
-    return select_block_m(weight.n, weight.k, weight.num_experts, num_tokens * top_k)
+    routed = num_tokens * top_k
+    if total_experts is not None:
+        if isinstance(total_experts, bool) or not isinstance(total_experts, int) or total_experts < weight.num_experts:
+            raise ValueError(
+                f"total_experts must be an int >= the weight's {weight.num_experts} experts, got {total_experts!r}"
+            )
+        routed = -(-routed * weight.num_experts // total_experts)
+    return select_block_m(weight.n, weight.k, weight.num_experts, routed)
 
 
 def w4a16_indexed(

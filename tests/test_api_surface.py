@@ -42,7 +42,8 @@ def test_signatures_match_the_reference():
         ("activation", P, E), ("weight", P, E), ("m_indices", P, E), ("outputs", K, None),
         ("enable_pdl", K, False)]
     assert _params(chord_b200.indexed_block_m) == [
-        ("weight", P, E), ("num_tokens", P, E), ("top_k", P, E), ("device", K, None)]
+        ("weight", P, E), ("num_tokens", P, E), ("top_k", P, E), ("device", K, None),
+        ("total_experts", K, None)]   # the last one is an extension (expert parallelism)
     assert _params(chord_b200.pack_w4a16) == [
         ("weight_uint4", P, E), ("weight_scale", P, E), ("packed", K, False)]
     # the schedule is not a public knob of `indexed`
@@ -72,6 +73,13 @@ def test_indexed_block_m_contract(native_lib):
         assert isinstance(bm, int) and bm % 8 == 0
     with pytest.raises(TypeError):
         indexed_block_m("not a weight", 4, 8)
+    # expert parallelism: 48 of 384 experts live here, so 256 tokens x top-8 bring about
+    # five rows per local expert, not forty
+    assert indexed_block_m(w, 256, 8, total_experts=384) == indexed_block_m(w, 32, 8)
+    assert indexed_block_m(w, 256, 8, total_experts=384) < indexed_block_m(w, 256, 8)
+    assert indexed_block_m(w, 256, 8, total_experts=48) == indexed_block_m(w, 256, 8)
+    with pytest.raises(ValueError):
+        indexed_block_m(w, 256, 8, total_experts=8)
 
 
 def test_argument_errors_before_any_gpu_work():
