@@ -452,12 +452,14 @@ def main():
                         "routed_rows": workload.routed},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "peak_kind": peak_kind,
-                         "kernel": "w4a16_gemm_kernel (gate_up + down launches)",
+                         "kernel": ("w4a16_decode_kernel" if workload.block_m <= 32
+                                    else "w4a16_gemm_kernel") + " (gate_up + down launches)",
                          "algorithmic_bytes_per_step": gemm_bytes,
-                         # dram__bytes_read+write of one ncu capture at batch 64 (853 MB for 34
-                         # reached experts), scaled by the experts this step reaches
-                         "traffic": 852.7e6 * workload.active / 34.0,
-                         "traffic_source": "profiles/w4a16_gemm_kernel_k25_ep8_decode.md"},
+                         # dram__bytes_read+write of one ncu capture of both launches at batch
+                         # 256 (1209.3 MB for 48 reached experts), scaled by the experts this
+                         # step reaches
+                         "traffic": 1209.3e6 * workload.active / 48.0,
+                         "traffic_source": "profiles/w4a16_decode_kernel_k25_ep8_decode.md"},
             "cpu_baseline": cpu,
             "e2e": {"value": e2e_ms * 1e3, "unit": "us", "h2d_bytes_per_step": workload.h2d_bytes,
                     "d2h_bytes_per_step": workload.d2h_bytes},
