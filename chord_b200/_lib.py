@@ -82,6 +82,8 @@ def _apply_env_options(lib: ctypes.CDLL) -> None:
         ("CHORD_B200_DEQUANT_GROUPS", "dequant_groups"),
         ("CHORD_B200_MAX_STAGES", "max_stages"),
         ("CHORD_B200_GRID", "grid_limit"),
+        ("CHORD_B200_KSPLIT", "ksplit"),
+        ("CHORD_B200_DECODE_KERNEL", "decode_kernel"),
     ):
         value = os.environ.get(env)
         if value is None:

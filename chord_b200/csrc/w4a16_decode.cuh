@@ -110,6 +110,7 @@ __device__ __forceinline__ TileInfo decode_tile_small(const GemmParams& p, const
     t.base = lo * p.max_m;
     t.mma_n = t.ntok <= 16 ? 16 : 32;
   }
+  t.rows = t.ntok;
   t.valid = t.expert >= 0 && t.expert < p.num_experts && t.ntok > 0;
   return t;
 }

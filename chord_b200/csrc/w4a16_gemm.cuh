@@ -144,6 +144,7 @@ struct GemmParams {
   int32_t w_stages;     // depth of the weight/scale ring
   int32_t x_stages;     // depth of the activation ring
   int32_t issuers;      // 1, 2 or 4 MMA issuers (and accumulators)
+  int32_t ksplit;       // single-issuer layouts: a second issuer takes the second K half of tiles of <= 128 tokens
   int32_t a_stages;     // depth of the TMEM A ring; accumulators start at column 64 * a_stages
   int32_t num_locks;
   const int32_t* sorted_ids;
@@ -163,11 +164,12 @@ struct GemmParams {
 struct TileInfo {
   int32_t n0;      // first weight row
   int32_t expert;
-  int32_t ntok;    // valid token slots in the tile
+  int32_t ntok;    // token slots of the tile that carry a row (one past the last one)
+  int32_t rows;    // token slots whose output rows the tile writes (contiguous: whole blocks)
   int32_t base;    // indexed: first sorted_ids slot; contiguous: first row; masked: first row of the group
   int32_t m0;      // masked: first row inside the group
   int32_t limit;   // masked: masked_m of the group
-  int32_t mma_n;   // MMA N of this tile (contiguous tiles are 128 or 256 tokens)
+  int32_t mma_n;   // MMA N of this tile: ntok rounded up to 16
   bool valid;
 };
 
@@ -268,6 +270,11 @@ struct __align__(16) GemmShared {
   // contiguous: M tiles after merging neighbouring 128-row blocks of one expert:
   // expert | first block << 15 | (256 rows ? 1 : 0) << 31
   uint32_t mtile[kMaxMTiles];
+  // contiguous, indexed: token slots of each M tile that carry a row (padding rows at
+  // the end of an expert's run, sentinels at the end of a routing block, do not): the
+  // tile's MMA runs with N = that count rounded up to 16, not with the full block.
+  uint16_t tile_rows[kMaxMTiles];
+  int32_t have_tile_rows;
 };
 
 __device__ __forceinline__ TileInfo decode_tile(const GemmParams& p, const GemmShared& sh,
@@ -281,13 +288,14 @@ __device__ __forceinline__ TileInfo decode_tile(const GemmParams& p, const GemmS
   t.mma_n = p.mma_n;
   if (p.mode == kModeIndexed) {
     t.expert = __ldg(p.expert_ids + mb);
-    t.ntok = p.tile_tokens;
+    t.ntok = sh.have_tile_rows ? static_cast<int32_t>(sh.tile_rows[mb]) : p.tile_tokens;
+    t.rows = t.ntok;
     t.base = mb * p.tile_tokens;
   } else if (p.mode == kModeContiguous) {
     const uint32_t info = sh.mtile[mb];
     t.expert = static_cast<int32_t>(info & 0x7FFFu);
-    t.ntok = (info >> 31) ? 256 : 128;
-    t.mma_n = t.ntok;
+    t.rows = (info >> 31) ? 256 : 128;
+    t.ntok = static_cast<int32_t>(sh.tile_rows[mb]);
     t.base = static_cast<int32_t>((info >> 15) & 0xFFFFu) * 128;
   } else {
     // Largest g with group_prefix[g] <= mb.
@@ -303,8 +311,10 @@ __device__ __forceinline__ TileInfo decode_tile(const GemmParams& p, const GemmS
     t.limit = mm;
     const int32_t left = mm - t.m0;
     t.ntok = left < p.tile_tokens ? left : p.tile_tokens;
+    t.rows = t.ntok;
     t.base = lo * p.max_m;
   }
+  t.mma_n = (t.ntok + 15) & ~15;
   t.valid = t.expert >= 0 && t.expert < p.num_experts && t.ntok > 0;
   return t;
 }
@@ -323,7 +333,7 @@ __device__ __forceinline__ int32_t x_row_of(const GemmParams& p, const TileInfo&
 
 // Output row written by token slot `slot`, or -1.
 __device__ __forceinline__ int32_t out_row_of(const GemmParams& p, const TileInfo& t, int32_t slot) {
-  if (slot >= t.ntok) return -1;
+  if (slot >= t.rows) return -1;
   if (p.mode == kModeIndexed) {
     const int32_t id = __ldg(p.sorted_ids + t.base + slot);
     return (id >= 0 && id < p.out_rows) ? id : -1;
@@ -385,6 +395,31 @@ struct StageCursor {
   }
 };
 
+// Activation ring cut into sub-slots of 128 token rows (both 64-wide K halves, 32 KB).
+// A stage of a tile of at most 128 tokens takes one sub-slot, a 256-token stage an
+// aligned pair (one sub-slot may be skipped to align), so that a launch mixing small and
+// large tiles gives the small ones a ring twice as deep.  Every party keeps a cursor
+// and one phase bit per sub-slot barrier of its own; all walk the same tile sequence.
+// A pair is tracked by the barriers of its even sub-slot alone (the MMA issuer is the
+// critical path of large tiles: no second wait or commit for it); the odd sub-slot's
+// barriers keep the state of its last use on its own, which the loader checks without
+// consuming it before it overwrites the memory.  That use is never outstanding when the
+// odd sub-slot is next taken on its own, because the ring always passes through the even
+// one (and so waits for the pair) first.
+struct XSubRing {
+  uint32_t next = 0;
+  uint32_t phases = 0;
+  __device__ __forceinline__ uint32_t take(bool pair, uint32_t count) {
+    if (pair && (next & 1u)) next = next + 1u == count ? 0u : next + 1u;
+    const uint32_t first = next;
+    next += pair ? 2u : 1u;
+    if (next >= count) next -= count;
+    return first;
+  }
+  __device__ __forceinline__ uint32_t phase(uint32_t slot) const { return (phases >> slot) & 1u; }
+  __device__ __forceinline__ void flip(uint32_t slot) { phases ^= 1u << slot; }
+};
+
 template <int kDequantGroups>
 __global__ void __launch_bounds__(32 * (12 + 4 * kDequantGroups), 1)
 w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_s,
@@ -412,8 +447,19 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
   // Accumulators: `ni` issuers x `d_bufs` buffers of `d_cols` columns each in the
   // 256 TMEM columns after the A ring; buffer d of issuer i starts at column
   // 64 * a_stages + (d * ni + i) * d_cols.
-  const uint32_t ni = static_cast<uint32_t>(p.issuers);
-  const uint32_t d_cols = static_cast<uint32_t>(p.mma_n);
+  // With `ksplit` (layouts whose token tile exceeds 64) there are two issuers that do
+  // not take turns: on tiles of at most 128 tokens issuer 0 takes the first 64-wide K
+  // half of every stage and issuer 1 the second, each into its own 128-column
+  // accumulator; on larger tiles issuer 0 does both halves into all 256 columns and
+  // issuer 1 only keeps the barriers' phases moving.  One tcgen05.mma costs its issuing
+  // thread ~100 cycles on a busy SM whatever its size, so a lone issuer caps small
+  // tiles at ~900 cycles per stage.
+  const bool ksplit = p.ksplit != 0;
+  // 256-token layouts with consecutive activation rows: sub-slot ring (see XSubRing).
+  const bool subslots = ksplit && p.x_load == kXLoadTiled && p.mma_n == 256;
+  constexpr uint32_t kSubBytes = 128u * 256u;
+  const uint32_t ni = ksplit ? 2u : static_cast<uint32_t>(p.issuers);
+  const uint32_t d_cols = ksplit ? 128u : static_cast<uint32_t>(p.mma_n);
   const uint32_t a_stages = static_cast<uint32_t>(p.a_stages);
   const uint32_t d_col0 = a_stages * kAColsPerStage;
   const uint32_t d_bufs = 2u * ni * d_cols <= kTmemCols - d_col0 ? 2u : 1u;
@@ -431,9 +477,9 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
     }
     // One arrival per gathering warp, or one transaction-count arrival.
     const uint32_t xfull_count = p.x_load == kXLoadCpAsync ? kHelperThreads / 32 : 1u;
-    for (uint32_t s = 0; s < x_stages; ++s) {
+    for (uint32_t s = 0; s < (subslots ? 2u * x_stages : x_stages); ++s) {
       ptx::mbar_init(ptx::smem_u32(&sh.xfull[s]), xfull_count);
-      ptx::mbar_init(ptx::smem_u32(&sh.xempty[s]), 1);
+      ptx::mbar_init(ptx::smem_u32(&sh.xempty[s]), ksplit ? 2 : 1);
     }
     for (uint32_t a = 0; a < 2 * a_stages; ++a) {
       ptx::mbar_init(ptx::smem_u32(&sh.afull[a]), 4);
@@ -474,6 +520,20 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
       padded = padded < 0 ? 0 : (padded > p.sorted_len ? p.sorted_len : padded);
       int32_t blocks = padded / p.tile_tokens;
       sh.m_blocks = blocks > p.expert_len ? p.expert_len : blocks;
+      sh.have_tile_rows = sh.m_blocks <= kMaxMTiles ? 1 : 0;
+    }
+    __syncthreads();
+    // One warp per routing block: one past the last slot whose id names a row.
+    if (sh.have_tile_rows) {
+      for (int32_t b = static_cast<int32_t>(warp); b < sh.m_blocks; b += static_cast<int32_t>(blockDim.x >> 5)) {
+        int32_t last = 0;
+        for (int32_t i = static_cast<int32_t>(lane); i < p.tile_tokens; i += 32) {
+          const int32_t id = __ldg(p.sorted_ids + b * p.tile_tokens + i);
+          if (id >= 0 && id < p.out_rows && id / p.top_k < p.x_rows) last = i + 1;
+        }
+        last = __reduce_max_sync(0xffffffffu, last);
+        if (lane == 0) sh.tile_rows[b] = static_cast<uint16_t>(last);
+      }
     }
   } else {
     // Expert of every 128-row block (its first row names it), then one thread merges
@@ -482,6 +542,17 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
     // never passes the read position.
     for (int32_t i = threadIdx.x; i < p.m_blocks; i += blockDim.x) {
       sh.mtile[i] = static_cast<uint32_t>(__ldg(p.m_indices + i * 128));
+    }
+    // One warp per block: one past its last row that belongs to an expert.
+    for (int32_t b = static_cast<int32_t>(warp); b < p.m_blocks; b += static_cast<int32_t>(blockDim.x >> 5)) {
+      int32_t last = 0;
+#pragma unroll
+      for (int32_t j = 0; j < 4; ++j) {
+        const int32_t i = 32 * j + static_cast<int32_t>(lane);
+        if (__ldg(p.m_indices + b * 128 + i) >= 0) last = i + 1;
+      }
+      last = __reduce_max_sync(0xffffffffu, last);
+      if (lane == 0) sh.tile_rows[b] = static_cast<uint16_t>(last);
     }
     __syncthreads();
     if (threadIdx.x == 0) {
@@ -494,6 +565,7 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
         }
         const bool pair = p.tile_tokens == 256 && i + 1 < p.m_blocks &&
                           static_cast<int32_t>(sh.mtile[i + 1]) == e;
+        sh.tile_rows[count] = pair ? static_cast<uint16_t>(128 + sh.tile_rows[i + 1]) : sh.tile_rows[i];
         sh.mtile[count++] = static_cast<uint32_t>(e) | (static_cast<uint32_t>(i) << 15) |
                             (pair ? 0x80000000u : 0u);
         i += pair ? 2 : 1;
@@ -560,6 +632,7 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
   } else if (warp < kFirstIssuerWarp) {
     // ------------------------------------------------ warps 2-3: activations --
     StageCursor cur;
+    XSubRing xring;
     bool ok = true;
     CHORD_PROF_INIT();
     if (p.x_load == kXLoadTiled) {
@@ -570,7 +643,29 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
         int32_t k_col = seg.kb * kBlockK;
         const int32_t x_row0 = t.base + t.m0;
         const int32_t boxes = (t.mma_n + p.x_box_rows - 1) / p.x_box_rows;
+        const bool pair = t.mma_n > 128;
         for (int32_t kb = seg.kb; kb < seg.ke; ++kb) {
+          if (subslots) {
+            const uint32_t s0 = xring.take(pair, 2u * x_stages);
+            if (!ptx::mbar_wait(ptx::smem_u32(&sh.xempty[s0]), xring.phase(s0) ^ 1u, abort_flag) ||
+                (pair && !ptx::mbar_wait(ptx::smem_u32(&sh.xempty[s0 + 1]), xring.phase(s0 + 1) ^ 1u,
+                                         abort_flag))) {  // odd half: checked, not consumed
+              ok = false;
+              break;
+            }
+            const uint32_t full = ptx::smem_u32(&sh.xfull[s0]);
+            const uint32_t xs = ptx::smem_u32(smem_x + s0 * kSubBytes);
+            const uint32_t half = pair ? kSubBytes : kSubBytes / 2;  // bytes of one K half
+            ptx::mbar_arrive_expect_tx(full, static_cast<uint32_t>(boxes) * kSubBytes);
+            for (int32_t b = 0; b < boxes; ++b) {
+              const uint32_t off = static_cast<uint32_t>(b) * (kSubBytes / 2);
+              ptx::tma_load_2d(xs + off, &tm_x, full, k_col, x_row0 + b * 128);
+              ptx::tma_load_2d(xs + half + off, &tm_x, full, k_col + 64, x_row0 + b * 128);
+            }
+            xring.flip(s0);
+            k_col += kBlockK;
+            continue;
+          }
           if (!ptx::mbar_wait(ptx::smem_u32(&sh.xempty[cur.s]), cur.ph ^ 1u, abort_flag)) {
             ok = false;
             break;
@@ -750,6 +845,7 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
       const uint64_t xdesc_half = x_half_bytes >> 4;
       uint64_t xdesc = xdesc0;
       StageCursor cur, acur;
+      XSubRing xring;
       uint32_t it = 0, segc = 0;
       bool ok = true;
       CHORD_PROF_INIT();
@@ -768,8 +864,74 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
         const uint32_t d_addr = tmem_base + d_col0 + (d * ni + me) * d_cols;
         const uint32_t idesc = ptx::idesc_bf16_f32(kBlockN, static_cast<uint32_t>(t.mma_n));
         uint32_t acc = 0;
+        const bool split = ksplit && t.mma_n <= 128;
         for (int32_t kb = seg.kb; kb < seg.ke; ++kb, ++it) {
-          if ((it & (ni - 1)) == me) {
+          if (ksplit) {
+            const uint32_t a = acur.s << 1;
+            const uint32_t aph = acur.ph;
+            CHORD_PROF_T(pt1);
+            uint32_t xslot = cur.s;       // barrier (and, with sub-slots, buffer) of this stage
+            uint64_t xd = xdesc, xd_half = xdesc_half;
+            const bool pair = subslots && t.mma_n > 128;
+            if (subslots) {
+              xslot = xring.take(pair, 2u * x_stages);
+              xd = xdesc0 + xslot * (kSubBytes >> 4);
+              xd_half = pair ? (kSubBytes >> 4) : (kSubBytes >> 5);
+              if (!ptx::mbar_wait(ptx::smem_u32(&sh.xfull[xslot]), xring.phase(xslot), abort_flag)) {
+                ok = false;
+                break;
+              }
+              xring.flip(xslot);
+            } else if (!ptx::mbar_wait(ptx::smem_u32(&sh.xfull[cur.s]), cur.ph, abort_flag)) {
+              ok = false;
+              break;
+            }
+            CHORD_PROF_ADD(2, pt1);
+            if (p.x_load == kXLoadCpAsync) ptx::fence_proxy_async();
+            const uint32_t a_addr = tmem_base + acur.s * kAColsPerStage;
+            const bool tail = k_tail_half && kb == k_iters - 1;
+            if (me == 0) {
+              CHORD_PROF_T(pt2);
+              if (!ptx::mbar_wait(ptx::smem_u32(&sh.afull[a]), aph, abort_flag)) {
+                ok = false;
+                break;
+              }
+              CHORD_PROF_ADD(3, pt2);
+              CHORD_PROF_T(pt3);
+              ptx::tc_fence_after();
+              ptx::mma_ts(d_addr, a_addr, xd, idesc, acc);
+              ptx::mma_ts(d_addr, a_addr + 8, xd + 2, idesc, 1);
+              ptx::mma_ts(d_addr, a_addr + 16, xd + 4, idesc, 1);
+              ptx::mma_ts(d_addr, a_addr + 24, xd + 6, idesc, 1);
+              acc = 1;
+              ptx::mma_commit(ptx::smem_u32(&sh.aempty[a]));
+              CHORD_PROF_ADD(4, pt3);
+            }
+            if (me == 0 ? !split : split) {
+              CHORD_PROF_T(pt4);
+              if (!ptx::mbar_wait(ptx::smem_u32(&sh.afull[a + 1]), aph, abort_flag)) {
+                ok = false;
+                break;
+              }
+              CHORD_PROF_ADD(3, pt4);
+              CHORD_PROF_T(pt5);
+              ptx::tc_fence_after();
+              if (!tail) {
+                const uint64_t xd1 = xd + xd_half;
+                ptx::mma_ts(d_addr, a_addr + 32, xd1, idesc, acc);
+                ptx::mma_ts(d_addr, a_addr + 40, xd1 + 2, idesc, 1);
+                ptx::mma_ts(d_addr, a_addr + 48, xd1 + 4, idesc, 1);
+                ptx::mma_ts(d_addr, a_addr + 56, xd1 + 6, idesc, 1);
+                acc = 1;
+              }
+              ptx::mma_commit(ptx::smem_u32(&sh.aempty[a + 1]));
+              CHORD_PROF_ADD(4, pt5);
+            }
+            // Both issuers account for the activation stage: a commit after MMAs of one's
+            // own, a plain arrival otherwise.
+            if (me == 0 || split) ptx::mma_commit(ptx::smem_u32(&sh.xempty[xslot]));
+            else ptx::mbar_arrive(ptx::smem_u32(&sh.xempty[xslot]));
+          } else if ((it & (ni - 1)) == me) {
             const uint32_t a = acur.s << 1;  // barrier of the first K half; the second is a + 1
             const uint32_t aph = acur.ph;
             CHORD_PROF_T(pt1);
@@ -998,7 +1160,8 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
       const uint32_t d = d_bufs == 2 ? (segc & 1u) : 0u;
       const uint32_t dph = d_bufs == 2 ? ((segc >> 1) & 1u) : (segc & 1u);
       ptx::named_bar_sync(1, 128);  // previous segment's out_row readers are done
-      for (int32_t c = et; c < t.mma_n; c += 128) sh.out_row[c] = out_row_of(p, t, c);
+      const int32_t row_slots = (t.rows + 15) & ~15;  // >= t.mma_n; beyond it: rows written as zeros
+      for (int32_t c = et; c < row_slots; c += 128) sh.out_row[c] = out_row_of(p, t, c);
       if (seg.type == kSegOwner && et == 0) {
         // Wait (bounded) until every other slice of this tile has published its partial.
         const int* lock = p.locks + blockIdx.x;
@@ -1031,12 +1194,22 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
       // Issuer i accumulated the stages it0 + j with (it0 + j) % ni == i; it took part
       // in this segment only if one of them falls inside it.
       const uint32_t seg_len = static_cast<uint32_t>(seg.ke - seg.kb);
-      for (int32_t c0 = 0; c0 < t.mma_n; c0 += 16) {
+      for (int32_t c0 = 0; c0 < row_slots; c0 += 16) {
         float acc[16];
 #pragma unroll
         for (int j = 0; j < 16; ++j) acc[j] = 0.0f;
-        for (uint32_t i = 0; i < ni; ++i) {
-          if (((i - it0) & (ni - 1)) >= seg_len) continue;
+        // Slots past the tile's MMA N hold padding rows of a contiguous block: the product
+        // of their all-zero activations is written without having been computed.
+        const bool computed = c0 < t.mma_n;
+        if (!computed && seg.type == kSegContrib) continue;
+        for (uint32_t i = 0; computed && i < ni; ++i) {
+          if (ksplit) {
+            // issuer 1 holds the second K halves of tiles of at most 128 tokens, unless the
+            // segment is nothing but the half-filled last stage
+            if (i == 1 && (t.mma_n > 128 || seg_len == (k_tail_half && seg.ke == k_iters ? 1u : 0u))) continue;
+          } else if (((i - it0) & (ni - 1)) >= seg_len) {
+            continue;
+          }
           uint32_t v[16];
           ptx::tmem_ld_32x32b_x16(d_addr + i * d_cols + c0, v);
           ptx::tmem_wait_ld();
@@ -1049,7 +1222,7 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
           for (int j = 0; j < 16; ++j) __stcg(dst + j * kBlockN, acc[j]);
           continue;
         }
-        if (seg.type == kSegOwner) {
+        if (seg.type == kSegOwner && computed) {
           for (int32_t peer = 1; peer <= seg.peer; ++peer) {
             const float* src = p.workspace + (blockIdx.x + peer) * ws_slot +
                                static_cast<size_t>(c0) * kBlockN + et;
