@@ -30,6 +30,7 @@ SIGNATURES = {
     "chord_b200_indexed_block_m": (_int, [_i64, _i64, _i64, _i64]),
     "chord_b200_masked_tile_m": (_int, [_i64]),
     "chord_b200_gemm_workspace_bytes": (_i64, [_i64]),
+    "chord_b200_indexed_workspace_bytes": (_i64, [_i64, _i64, _i64]),
     "chord_b200_gemm_lock_words": (_int, []),
     "chord_b200_schedule_segments": (_i64, [_i64, _i64, _i64, _i64, _ptr, _i64]),
     "chord_b200_indexed": (_int, [_ptr, _ptr, _ptr, _ptr, _i64, _ptr, _i64, _ptr, _ptr, _ptr, _i64,
@@ -83,6 +84,7 @@ def _apply_env_options(lib: ctypes.CDLL) -> None:
         ("CHORD_B200_MAX_STAGES", "max_stages"),
         ("CHORD_B200_GRID", "grid_limit"),
         ("CHORD_B200_KSPLIT", "ksplit"),
+        ("CHORD_B200_PREGATHER", "pregather"),
         ("CHORD_B200_DECODE_KERNEL", "decode_kernel"),
     ):
         value = os.environ.get(env)

@@ -78,6 +78,9 @@ int chord_b200_set_option(const char* name, int64_t value) {
     if (value != 0 && value != 128 && value != 256)
       return fail(kInvalidArgument, "contiguous_tile must be 0, 128 or 256");
     o.contiguous_tile = static_cast<int>(value);
+  } else if (!std::strcmp(name, "pregather")) {
+    if (value != 0 && value != 1) return fail(kInvalidArgument, "pregather must be 0 or 1");
+    o.pregather = static_cast<int>(value);
   } else if (!std::strcmp(name, "ksplit")) {
     if (value != 0 && value != 1) return fail(kInvalidArgument, "ksplit must be 0 or 1");
     o.ksplit = static_cast<int>(value);

@@ -153,6 +153,43 @@ int launch_with_groups(const CUtensorMap& tm_w, const CUtensorMap& tm_s, const C
   return kOk;
 }
 
+// `indexed` with routing blocks of 64 rows or more: the routed activation rows are first
+// copied into slot order (row s of the copy = the row sorted_ids[s] names, zeros for a
+// sentinel), so that the GEMM loads them as TMA boxes like `contiguous` does.  Two
+// gathering warps cannot feed 64..256-row tiles: at 85 rows per tile they were the
+// bottleneck (2400 of 2600 cycles per stage), at 256 rows seven times slower than the
+// MMAs.  The copy costs one read and one write of the routed rows (HBM-bound, <2 % of
+// the GEMM's time at these sizes).  One warp per slot.
+__global__ void __launch_bounds__(256)
+gather_routed_rows_kernel(const __nv_bfloat16* __restrict__ x, const int32_t* __restrict__ sorted_ids,
+                          const int32_t* __restrict__ num_tokens_padded, __nv_bfloat16* __restrict__ out,
+                          int32_t sorted_len, int32_t x_rows, int32_t out_rows, int32_t top_k, int32_t k) {
+  int32_t padded = __ldg(num_tokens_padded);
+  padded = padded < 0 ? 0 : (padded > sorted_len ? sorted_len : padded);
+  const int32_t lane = threadIdx.x & 31;
+  const int32_t warps = (gridDim.x * blockDim.x) >> 5;
+  for (int32_t slot = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; slot < padded; slot += warps) {
+    const int32_t id = __ldg(sorted_ids + slot);
+    const int32_t row = (id >= 0 && id < out_rows) ? id / top_k : x_rows;
+    uint4* dst = reinterpret_cast<uint4*>(out + static_cast<size_t>(slot) * k);
+    if (row < x_rows) {
+      const uint4* src = reinterpret_cast<const uint4*>(x + static_cast<size_t>(row) * k);
+      for (int32_t i = lane; i < k / 8; i += 32) dst[i] = __ldg(src + i);
+    } else {
+      for (int32_t i = lane; i < k / 8; i += 32) dst[i] = make_uint4(0, 0, 0, 0);
+    }
+  }
+}
+
+// Workspace of an `indexed` launch: the stream-K partials, then (1024-byte aligned) the
+// slot-ordered copy of the activations when the routing blocks are large enough for it.
+int64_t stream_k_bytes(int grid, int mma_n) {
+  const int64_t general = static_cast<int64_t>(grid) * kBlockN * mma_n * 4;
+  return (general + 1023) / 1024 * 1024;
+}
+
+bool pregather_applies(int mma_n) { return options().pregather != 0 && mma_n >= 64; }
+
 // Token tiles of at most 32 rows (indexed, masked) have a kernel of their own, in which
 // every warpgroup of a CTA is an independent worker with a lock word and a scratch
 // slot of its own: four times as many of each as the general kernel needs.
@@ -242,6 +279,21 @@ int launch_gemm(GemmParams p, const void* x, const int32_t* packed, const void* 
     p.num_locks = static_cast<int32_t>(num_locks);
     return launch_decode(p, dev, packed, scale, grid, static_cast<cudaStream_t>(stream));
   }
+  p.x_load = p.mode == kModeIndexed ? (options().x_load == 1 ? kXLoadGather4 : kXLoadCpAsync)
+                                    : kXLoadTiled;
+  // Large routing blocks: slot-ordered copy of the activations behind the stream-K
+  // partials, if the caller's workspace has room for it (chord_b200_indexed_workspace_bytes).
+  __nv_bfloat16* gathered = nullptr;
+  if (p.mode == kModeIndexed && pregather_applies(p.mma_n) && p.sorted_len > 0) {
+    const int64_t offset = stream_k_bytes(grid, p.mma_n);
+    const int64_t bytes = static_cast<int64_t>(p.sorted_len) * p.k * 2;
+    if (workspace_bytes >= offset + bytes && static_cast<int64_t>(p.sorted_len) * p.k < (1ll << 31) &&
+        (reinterpret_cast<uintptr_t>(p.workspace) & 15u) == 0 &&
+        (reinterpret_cast<uintptr_t>(x) & 15u) == 0) {
+      gathered = reinterpret_cast<__nv_bfloat16*>(reinterpret_cast<uint8_t*>(p.workspace) + offset);
+      p.x_load = kXLoadTiled;
+    }
+  }
   p.x_stages = pick_x_stages(p.mma_n);
   p.w_stages = pick_w_stages(dev, p.mma_n, p.x_stages);
   CHORD_REQUIRE(p.w_stages >= 2, "token tile %d leaves room for fewer than two pipeline stages",
@@ -256,10 +308,9 @@ int launch_gemm(GemmParams p, const void* x, const int32_t* packed, const void* 
   if (options().issuers > 0 && options().issuers * p.mma_n <= 256) p.issuers = options().issuers;
   // Single-issuer layouts with consecutive activation rows get a second issuer for the
   // second K half of tiles of at most 128 tokens (two 128-column accumulators in the
-  // same 256 columns).  Not for `indexed`: there the 128-token layout keeps its
-  // double-buffered accumulator instead, which measured 7 % faster on the 384-expert
-  // layer (85 rows per expert).
-  p.ksplit = (p.issuers == 1 && options().ksplit != 0 && p.mode != kModeIndexed) ? 1 : 0;
+  // same 256 columns).  Not where two warps gather the rows: there the 128-token layout
+  // keeps its double-buffered accumulator instead, which measured 7 % faster.
+  p.ksplit = (p.issuers == 1 && options().ksplit != 0 && p.x_load == kXLoadTiled) ? 1 : 0;
   const int acc_cols = p.ksplit ? 256 : p.issuers * p.mma_n;
   p.a_stages = 2 * acc_cols <= 128 ? 6 : 4;
   if (options().a_stages > 0 && (512 - 64 * options().a_stages) >= acc_cols) {
@@ -277,8 +328,6 @@ int launch_gemm(GemmParams p, const void* x, const int32_t* packed, const void* 
   CHORD_REQUIRE(p.a_stages >= turn && p.w_stages >= groups && p.x_stages >= p.issuers,
                 "internal: ring depths %d/%d/%d too small for %d groups and %d issuers",
                 p.a_stages, p.w_stages, p.x_stages, groups, p.issuers);
-  p.x_load = p.mode == kModeIndexed ? (options().x_load == 1 ? kXLoadGather4 : kXLoadCpAsync)
-                                    : kXLoadTiled;
   p.num_locks = static_cast<int32_t>(num_locks);
   CHORD_REQUIRE(p.locks != nullptr && num_locks >= grid,
                 "stream-K needs a zeroed locks buffer of at least %d lock words, got %lld", grid,
@@ -290,6 +339,7 @@ int launch_gemm(GemmParams p, const void* x, const int32_t* packed, const void* 
 
   // 256-token layouts load consecutive rows as boxes of 128 (sub-slot ring of the kernel).
   p.x_box_rows = (p.mode == kModeContiguous || p.mma_n == 256) ? 128 : p.mma_n;
+  if (p.x_load != kXLoadTiled) p.x_box_rows = p.mma_n;
   CUtensorMap tm_w, tm_s, tm_x;
   if (int rc = make_map_2d(&tm_w, packed, CU_TENSOR_MAP_DATA_TYPE_INT32, 4,
                            static_cast<uint64_t>(p.n) * 2,
@@ -301,8 +351,19 @@ int launch_gemm(GemmParams p, const void* x, const int32_t* packed, const void* 
                            static_cast<uint64_t>(p.num_experts) * (p.k / 32), kBlockN,
                            kBlockK / 32, CU_TENSOR_MAP_SWIZZLE_NONE))
     return rc;
-  if (int rc = make_map_2d(&tm_x, x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
-                           static_cast<uint64_t>(p.k), static_cast<uint64_t>(p.x_rows), 64,
+  if (gathered != nullptr) {
+    const int warps_needed = p.sorted_len;
+    const int blocks = warps_needed / 8 + 1 < 8 * dev.sm_count ? warps_needed / 8 + 1 : 8 * dev.sm_count;
+    gather_routed_rows_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        p.x, p.sorted_ids, p.num_tokens_padded, gathered, p.sorted_len, p.x_rows, p.out_rows, p.top_k,
+        p.k);
+    CHORD_CUDA(cudaGetLastError());
+  }
+  const void* x_base = gathered != nullptr ? static_cast<const void*>(gathered) : x;
+  const uint64_t x_map_rows = gathered != nullptr ? static_cast<uint64_t>(p.sorted_len)
+                                                  : static_cast<uint64_t>(p.x_rows);
+  if (int rc = make_map_2d(&tm_x, x_base, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+                           static_cast<uint64_t>(p.k), x_map_rows, 64,
                            p.x_load == kXLoadTiled ? static_cast<uint32_t>(p.x_box_rows) : 1u,
                            CU_TENSOR_MAP_SWIZZLE_128B))
     return rc;
@@ -383,6 +444,21 @@ int64_t chord_b200_gemm_workspace_bytes(int64_t tile_tokens) {
   const int mma_n = chord::round_up16(tile_tokens);
   if (mma_n <= chord::kDecMaxTokens) return chord::decode_workspace_bytes(grid, mma_n);
   return static_cast<int64_t>(grid) * chord::kBlockN * mma_n * 4;
+}
+
+int64_t chord_b200_indexed_workspace_bytes(int64_t block_m, int64_t sorted_len, int64_t k) {
+  chord::DeviceInfo dev;
+  if (chord::current_device_info(&dev)) return -1;
+  if (block_m <= 0 || block_m > chord::kMaxTileTokens || sorted_len < 0 || k <= 0) {
+    chord::fail(chord::kInvalidArgument, "bad workspace query");
+    return -1;
+  }
+  const int grid = chord::grid_size(dev);
+  const int mma_n = chord::round_up16(block_m);
+  if (mma_n <= chord::kDecMaxTokens) return chord::decode_workspace_bytes(grid, mma_n);
+  int64_t bytes = chord::stream_k_bytes(grid, mma_n);
+  if (chord::pregather_applies(mma_n)) bytes += sorted_len * k * 2;
+  return bytes;
 }
 
 int chord_b200_gemm_lock_words(void) {

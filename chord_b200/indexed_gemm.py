@@ -42,10 +42,12 @@ def default_locks(device: torch.device) -> torch.Tensor:
     return locks
 
 
-def gemm_scratch(device: torch.device, tile_tokens: int, locks: torch.Tensor | None):
-    """(locks, workspace) for one GEMM launch.  The FP32 stream-K workspace comes
-    from torch's caching allocator on every call, as in the reference's launcher
-    (csrc/launcher/launcher.cpp:110-123): stream-ordered and graph-pool safe."""
+def gemm_scratch(device: torch.device, tile_tokens: int, locks: torch.Tensor | None,
+                 sorted_len: int = 0, k: int = 0):
+    """(locks, workspace) for one GEMM launch.  The workspace (FP32 stream-K partials
+    and, for `indexed` with large routing blocks, the slot-ordered copy of the routed
+    rows) comes from torch's caching allocator on every call, as in the reference's
+    launcher (csrc/launcher/launcher.cpp:110-123): stream-ordered and graph-pool safe."""
     lib = _lib.load()
     need_words = lib.chord_b200_gemm_lock_words()
     if locks is None:
@@ -54,7 +56,10 @@ def gemm_scratch(device: torch.device, tile_tokens: int, locks: torch.Tensor | N
         raise RuntimeError(
             f"locks has {locks.numel()} lock words, this launch needs at least {need_words}"
         )
-    ws_bytes = lib.chord_b200_gemm_workspace_bytes(tile_tokens)
+    if sorted_len > 0:
+        ws_bytes = lib.chord_b200_indexed_workspace_bytes(tile_tokens, sorted_len, k)
+    else:
+        ws_bytes = lib.chord_b200_gemm_workspace_bytes(tile_tokens)
     if ws_bytes < 0:
         raise ValueError(_lib.last_error())
     workspace = torch.empty(ws_bytes // 4, dtype=torch.float32, device=device)
@@ -229,7 +234,7 @@ def w4a16_indexed(
 
     lib = _lib.load()
     with torch.cuda.device(device):
-        locks, workspace, ws_bytes = gemm_scratch(device, block_m, locks)
+        locks, workspace, ws_bytes = gemm_scratch(device, block_m, locks, sorted_ids.numel(), shape_k)
         _lib.check(lib.chord_b200_indexed(
             inputs.data_ptr(), packed.data_ptr(), scale.data_ptr(),
             sorted_ids.data_ptr(), sorted_ids.numel(), expert_ids.data_ptr(), expert_ids.numel(),

@@ -78,6 +78,15 @@ int chord_b200_masked_tile_m(int64_t expected_m);
  * launcher, launcher.cpp:110-123).  Returns < 0 on error. */
 int64_t chord_b200_gemm_workspace_bytes(int64_t tile_tokens);
 
+/* Bytes of scratch chord_b200_indexed wants for routing blocks of `block_m` rows,
+ * `sorted_len` routing slots and reduction depth `k`: the stream-K scratch above plus,
+ * for blocks of 64 rows or more, room for a copy of the routed activation rows in slot
+ * order (sorted_len * k BF16), which lets the kernel load them as TMA boxes.  A caller
+ * that passes only chord_b200_gemm_workspace_bytes() still gets a correct, slower
+ * launch (rows gathered inside the kernel).  No counterpart in the reference, whose
+ * launcher sizes its own scratch (launcher.cpp:110-123).  Returns < 0 on error. */
+int64_t chord_b200_indexed_workspace_bytes(int64_t block_m, int64_t sorted_len, int64_t k);
+
 /* Lock words a GEMM launch touches on the current device (all left zero).
  * The reference needs grid + grid/10 (launcher.cpp:95-109). */
 int chord_b200_gemm_lock_words(void);
@@ -101,7 +110,8 @@ int64_t chord_b200_schedule_segments(int64_t tiles, int64_t k, int64_t grid, int
  *  num_tokens_padded int32 [1], read on the device
  *  out               bf16 [m * top_k, n]; rows no id names are left untouched
  *  locks             int32 [num_locks] all zero on entry, all zero on exit
- *  workspace         FP32 scratch of chord_b200_gemm_workspace_bytes(block_m)
+ *  workspace         scratch of chord_b200_indexed_workspace_bytes(block_m, sorted_len, k)
+ *                    (at least chord_b200_gemm_workspace_bytes(block_m)), 16-byte aligned
  *  status            optional int32 word; a kernel that gives up on a bounded
  *                    wait ORs a nonzero code into it instead of hanging
  *  block_m           multiple of 8, at most 256 */
