@@ -447,6 +447,13 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
           scales[1] = ptx::lds64<256>(st + s_off);
           __syncwarp();
           if (lane == 0) ptx::mbar_arrive(wempty0 + cur.s * 8u);
+          // The operand slot is free once the MMAs of its previous use have completed.
+          // Waited for here, before the dequantised values exist: with thirty-two of them
+          // live, the wait's out-of-line slow path costs a register shuffle.
+          CHORD_PROF_T(pt2);
+          const uint32_t afree = afree0 + slot.s * 8u;
+          ok = ptx::mbar_wait_warp(afree, slot.ph ^ 1u, abort_flag);
+          CHORD_PROF_ADD(3, pt2);
           uint32_t lo[16], hi[16];
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
@@ -469,11 +476,6 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
             }
           }
           CHORD_PROF_ADD(2, pt1);
-          // The operand slot is free once the MMAs of its previous use have completed.
-          CHORD_PROF_T(pt2);
-          const uint32_t afree = afree0 + slot.s * 8u;
-          ok = ptx::mbar_wait_warp(afree, slot.ph ^ 1u, abort_flag);
-          CHORD_PROF_ADD(3, pt2);
           if (ok) {
             CHORD_PROF_T(pt3);
             ptx::tc_fence_after();
