@@ -140,3 +140,33 @@ def test_grouped_argument_checks(device):
     with pytest.raises(ValueError, match="m_indices"):
         chord_b200.contiguous(torch.zeros((128, 64), dtype=torch.bfloat16, device=device), w,
                               torch.zeros(64, dtype=torch.int32, device=device))
+
+
+@pytest.mark.parametrize("option,value", [("ksplit", 0), ("contiguous_tile", 128), ("decode_kernel", 0)])
+def test_grouped_kernel_variants(device, option, value):
+    """Without the second MMA issuer / without merged 256-token tiles / with small masked
+    tiles on the general kernel: same results within tolerance."""
+    import chord_b200
+    from chord_b200 import _lib
+
+    defaults = {"ksplit": 1, "contiguous_tile": 0, "decode_kernel": 1}
+    ccase = make_contiguous_case([5, 300, 0, 128, 77, 513], 512, 640, seed=31)
+    mcase = make_masked_case(6, 200, 256, 384, 16, seed=32)
+    mcase["masked_m"] = torch.tensor([0, 3, 16, 33, 150, 200], dtype=torch.int32)
+    _lib.set_option(option, value)
+    try:
+        w = chord_b200.pack_w4a16(ccase["codes"].to(device), ccase["scale"].to(device))
+        out = torch.full((ccase["x2"].size(0), 512), float("nan"), dtype=torch.bfloat16, device=device)
+        chord_b200.contiguous(ccase["x2"].to(device), w, ccase["m_indices"].to(device), outputs=out)
+        _status_ok(device)
+        _compare(out, O.reference_contiguous(ccase["x2"], ccase["codes"], ccase["scale"], ccase["m_indices"]))
+        for expected_m in (16, 200):
+            wm = chord_b200.pack_w4a16(mcase["codes"].to(device), mcase["scale"].to(device))
+            mout = torch.full((6 * 200, 256), float("nan"), dtype=torch.bfloat16, device=device)
+            chord_b200.masked(mcase["x3"].to(device), wm, mcase["masked_m"].to(device), expected_m,
+                              outputs=mout)
+            _status_ok(device)
+            ref = O.reference_masked(mcase["x3"], mcase["codes"], mcase["scale"], mcase["masked_m"])
+            _compare(mout, ref.reshape(6 * 200, 256))
+    finally:
+        _lib.set_option(option, defaults[option])

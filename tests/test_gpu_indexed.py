@@ -79,24 +79,63 @@ def test_indexed_matches_oracle(device, name):
     check_against_oracle(out, case)
 
 
-@pytest.mark.parametrize("option,value", [("x_load", 1), ("dequant_groups", 4), ("issuers", 1),
-                                          ("max_stages", 2), ("grid_limit", 5)])
-def test_kernel_variants_agree_bit_for_bit(device, option, value):
-    """Gather by TMA gather4 instead of cp.async, four dequant groups, one issuer, a
-    shallow pipeline, a five-CTA grid: the schedule changes, the numbers must not
-    (except the accumulation split, which stays within tolerance)."""
+OPTION_DEFAULTS = {"dequant_groups": 2, "decode_kernel": 1, "ksplit": 1, "pregather": 1}
+
+
+def _with_options(device, case, options):
     from chord_b200 import _lib
 
-    case = make_indexed_case(num_experts=8, n=1024, k=512, m=64, top_k=2, block_m=16, seed=3)
-    base, _ = run_case(device, case)
-    _lib.set_option(option, value)
+    for name, value in options.items():
+        _lib.set_option(name, value)
     try:
         out, _ = run_case(device, case)
     finally:
-        _lib.set_option(option, {"dequant_groups": 2}.get(option, 0))
+        for name in options:
+            _lib.set_option(name, OPTION_DEFAULTS.get(name, 0))
+    return out
+
+
+@pytest.mark.parametrize("option,value", [("x_load", 1), ("dequant_groups", 4), ("issuers", 1),
+                                          ("max_stages", 2), ("grid_limit", 5)])
+def test_kernel_variants_agree_bit_for_bit(device, option, value):
+    """General kernel (the decode-sized one switched off): gather by TMA gather4 instead
+    of cp.async, four dequant groups, one issuer, a shallow pipeline, a five-CTA grid:
+    the schedule changes, the numbers must not (except the accumulation split, which
+    stays within tolerance)."""
+    case = make_indexed_case(num_experts=8, n=1024, k=512, m=64, top_k=2, block_m=16, seed=3)
+    base = _with_options(device, case, {"decode_kernel": 0})
+    out = _with_options(device, case, {"decode_kernel": 0, option: value})
+    check_against_oracle(base, case)
     check_against_oracle(out, case)
     if option in ("x_load", "max_stages"):
         assert torch.equal(out.view(torch.int16), base.view(torch.int16))
+
+
+@pytest.mark.parametrize("name", ["config1", "tiny", "block8", "block24_odd_shapes"])
+@pytest.mark.parametrize("option,value", [("max_stages", 4), ("grid_limit", 5), ("decode_kernel", 0)])
+def test_decode_kernel_variants(device, name, option, value):
+    """Token tiles of at most 32 rows run on the decode-sized kernel by default; a shallow
+    ring and a five-CTA grid (every tile through stream-K) must not change a bit, and the
+    general kernel must agree within tolerance."""
+    case = make_indexed_case(**CASES[name])
+    base, _ = run_case(device, case)
+    out = _with_options(device, case, {option: value})
+    check_against_oracle(base, case)
+    check_against_oracle(out, case)
+    if option == "max_stages":
+        assert torch.equal(out.view(torch.int16), base.view(torch.int16))
+
+
+@pytest.mark.parametrize("name", ["block64", "block128", "block256"])
+def test_routed_rows_copied_or_gathered_in_kernel(device, name):
+    """Blocks of 64+ rows: the slot-ordered copy of the routed rows (default) and the
+    in-kernel gather (the path a caller with the small workspace gets) both match the
+    oracle; so does the copy path without the second MMA issuer."""
+    case = make_indexed_case(**CASES[name])
+    copied, _ = run_case(device, case)
+    check_against_oracle(copied, case)
+    check_against_oracle(_with_options(device, case, {"pregather": 0}), case)
+    check_against_oracle(_with_options(device, case, {"ksplit": 0}), case)
 
 
 def test_golden_fixture(device):
@@ -134,37 +173,43 @@ def test_deterministic_and_locks_reused(device):
     check_against_oracle(outs[0], case)
 
 
-@pytest.mark.parametrize("groups", [2, 4])
-def test_repeatable_with_every_group_count(device, groups):
-    """Ten launches, stream-K on every tile, 2 and 4 dequant groups (which also changes
-    the number of MMA issuers and the depth of the operand ring): bit-equal every time.
-    Guards the rule that ring depths are multiples of the parties taking turns on them."""
+@pytest.mark.parametrize("groups,decode_kernel", [(2, 0), (4, 0), (2, 1)])
+def test_repeatable_with_every_group_count(device, groups, decode_kernel):
+    """Ten launches, stream-K on every tile: bit-equal every time, on the general kernel
+    with 2 and 4 dequant groups (which also changes the number of MMA issuers and the
+    depth of the operand ring; guards the rule that ring depths are multiples of the
+    parties taking turns on them) and on the decode-sized kernel."""
     from chord_b200 import _lib
 
     case = make_indexed_case(num_experts=6, n=512, k=7168, m=12, top_k=2, block_m=16, seed=26)
     _lib.set_option("dequant_groups", groups)
+    _lib.set_option("decode_kernel", decode_kernel)
     try:
         outs = [run_case(device, case)[0].clone() for _ in range(10)]
     finally:
         _lib.set_option("dequant_groups", 2)
+        _lib.set_option("decode_kernel", 1)
     check_against_oracle(outs[0], case)
     for other in outs[1:]:
         assert torch.equal(other.view(torch.int16), outs[0].view(torch.int16))
 
 
-def test_stream_k_split_matches_whole_tiles(device):
+@pytest.mark.parametrize("decode_kernel", [1, 0])
+def test_stream_k_split_matches_whole_tiles(device, decode_kernel):
     """Few tiles on many CTAs forces every tile through the stream-K reduction; a
     one-CTA grid computes whole tiles.  FP32 partials summed once: nearly all outputs
     are bit-equal (the reference asks for >= 99.5 %, tests/test_w4a16_indexed.py:1284)."""
     from chord_b200 import _lib
 
     case = make_indexed_case(num_experts=2, n=256, k=7168, m=6, top_k=1, block_m=16, seed=22)
-    split, _ = run_case(device, case)
-    _lib.set_option("grid_limit", 1)
+    _lib.set_option("decode_kernel", decode_kernel)
     try:
+        split, _ = run_case(device, case)
+        _lib.set_option("grid_limit", 1)
         whole, _ = run_case(device, case)
     finally:
         _lib.set_option("grid_limit", 0)
+        _lib.set_option("decode_kernel", 1)
     check_against_oracle(split, case)
     check_against_oracle(whole, case)
     a, b = split.float().cpu(), whole.float().cpu()
