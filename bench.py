@@ -54,6 +54,9 @@ def parse_args():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--all-batches", action="store_true",
                     help="also time batches 1, 16 and 64 (reported under `batches`)")
+    ap.add_argument("--grouped", action="store_true",
+                    help="also time the prefill (contiguous) and masked configurations "
+                         "(reported under `prefill` and `masked`)")
     return ap.parse_args()
 
 
@@ -341,6 +344,87 @@ def ep_layer_bench(device, rank, world, steps, warmup):
     return result
 
 
+# ------------------------------------------------- prefill / masked side lines --
+
+def _event_us(fn, reps=10, warmup=3):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(reps):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn()
+        b.record()
+        torch.cuda.synchronize()
+        times.append(a.elapsed_time(b) * 1e3)
+    times.sort()
+    return times[len(times) // 2]
+
+
+def grouped_bench(device, w13, w2):
+    """BASELINE configurations 3 and 4 on the weights of the decode workload.
+
+    Prefill: 8192 tokens, top-8 by multinomial over 384 experts whose popularity is drawn
+    from Dirichlet(0.5) (seeded), rows of the 48 local experts kept, grouped per expert and
+    padded to 128; `contiguous` gate_up -> SiLU*mul -> `contiguous` down.  Masked: 24 local
+    experts, [24, 256, K] activations, masked_m ~ Poisson(expected_m) clipped to 256."""
+    import chord_b200
+    from chord_b200.packing import PreparedWeight
+
+    peaks = json.loads((ROOT / "MEASURED_PEAKS.json").read_text()) if (ROOT / "MEASURED_PEAKS.json").exists() else {}
+    tensor_peak = float(peaks.get("bf16_tflops", 1590.0))
+    g = torch.Generator().manual_seed(3)
+    torch.manual_seed(3)
+    popularity = torch.distributions.Dirichlet(torch.full((EXPERTS_TOTAL,), 0.5)).sample()
+    topk = torch.multinomial(popularity.expand(8192, EXPERTS_TOTAL), TOP_K, replacement=False, generator=g)
+    counts = [int((topk == e).sum()) for e in range(LOCAL_EXPERTS)]
+    idx = []
+    for e, c in enumerate(counts):
+        idx += [e] * c + [-1] * ((c + 127) // 128 * 128 - c)
+    m_indices = torch.tensor(idx, dtype=torch.int32, device=device)
+    m, valid = m_indices.numel(), sum(counts)
+    x = torch.randn((m, HIDDEN), device=device).to(torch.bfloat16)
+    x[m_indices < 0] = 0
+    gate_up = torch.empty((m, 2 * INTER), dtype=torch.bfloat16, device=device)
+    hidden = torch.empty((m, INTER), dtype=torch.bfloat16, device=device)
+    out = torch.empty((m, HIDDEN), dtype=torch.bfloat16, device=device)
+    us_gate = _event_us(lambda: chord_b200.contiguous(x, w13, m_indices, outputs=gate_up))
+    us_act = _event_us(lambda: chord_b200.silu_mul(gate_up, outputs=hidden))
+    us_down = _event_us(lambda: chord_b200.contiguous(hidden, w2, m_indices, outputs=out))
+    flops = 2.0 * valid * (2 * INTER * HIDDEN + HIDDEN * INTER)
+    tflops = flops / ((us_gate + us_down) * 1e-6) / 1e12
+    prefill = {
+        "workload": "k2.5_prefill_contiguous_8192_tokens_top8_dirichlet0.5", "rows_valid": valid,
+        "rows_padded": m, "experts_reached": sum(c > 0 for c in counts),
+        "gate_up_us": us_gate, "silu_mul_us": us_act, "down_us": us_down,
+        "tflops_valid_rows": tflops,
+        "roofline": {"bound": "tensor", "achieved": tflops, "peak": tensor_peak, "unit": "TFLOP/s",
+                     "frac": tflops / tensor_peak, "peak_kind": "measured" if peaks else "fallback"},
+    }
+    masked = []
+    groups = 24
+    wa = PreparedWeight(w13.packed[:groups], w13.scale[:groups], w13.n, w13.k, groups)
+    wb = PreparedWeight(w2.packed[:groups], w2.scale[:groups], w2.n, w2.k, groups)
+    for expected_m in (8, 32, 128):
+        gm = torch.Generator().manual_seed(expected_m)
+        masked_m = torch.poisson(torch.full((groups,), float(expected_m)), generator=gm).clamp(0, 256)
+        masked_m = masked_m.to(torch.int32)
+        rows, active = int(masked_m.sum()), int((masked_m > 0).sum())
+        mm = masked_m.to(device)
+        x3 = torch.randn((groups, 256, HIDDEN), device=device).to(torch.bfloat16)
+        h3 = torch.randn((groups, 256, INTER), device=device).to(torch.bfloat16)
+        o1 = torch.empty((groups * 256, 2 * INTER), dtype=torch.bfloat16, device=device)
+        o2 = torch.empty((groups * 256, HIDDEN), dtype=torch.bfloat16, device=device)
+        us1 = _event_us(lambda: chord_b200.masked(x3, wa, mm, expected_m, outputs=o1))
+        us2 = _event_us(lambda: chord_b200.masked(h3, wb, mm, expected_m, outputs=o2))
+        nbytes = traffic_bytes(active, 2 * INTER, HIDDEN, rows, rows) + traffic_bytes(active, HIDDEN, INTER, rows, rows)
+        masked.append({"groups": groups, "expected_m": expected_m, "rows": rows, "gate_up_us": us1,
+                       "down_us": us2, "gbs": nbytes / ((us1 + us2) * 1e-6) / 1e9,
+                       "tflops": 2.0 * rows * 3 * INTER * HIDDEN / ((us1 + us2) * 1e-6) / 1e12})
+    return prefill, masked
+
+
 # ----------------------------------------------------------------------- main --
 
 def run_reference_arm(args, rank, world):
@@ -424,6 +508,10 @@ def main():
                                "block_m": wl.block_m,
                                "gemm_gbs": gemm_bytes / ((k_us[0] + k_us[2]) * 1e-6) / 1e9 if wl.active else None}
 
+    prefill = masked = None
+    if args.grouped:
+        prefill, masked = grouped_bench(device, w13, w2)
+
     ep_layer = None
     if not args.no_ep_layer:
         ep_layer = ep_layer_bench(device, rank, world, max(3, min(args.steps, 5)), 3)
@@ -468,6 +556,8 @@ def main():
         }
         if batches:
             line["batches"] = batches
+        if prefill is not None:
+            line["prefill"], line["masked"] = prefill, masked
         if ep_layer is not None:
             line["ep_layer"] = ep_layer
         print(json.dumps(line))

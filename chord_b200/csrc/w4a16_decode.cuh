@@ -457,31 +457,21 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
           uint32_t lo[16], hi[16];
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
-            const uint2 sc = scales[i >> 1];
-            // sc.x = {slab A row r, slab A row r+8}; sc.y = same for slab B.
-            const uint32_t a_lo = __byte_perm(sc.x, 0, 0x1010);
-            const uint32_t a_hi = __byte_perm(sc.x, 0, 0x3232);
-            const uint32_t b_lo = __byte_perm(sc.y, 0, 0x1010);
-            const uint32_t b_hi = __byte_perm(sc.y, 0, 0x3232);
-            if (DEC_ABLATE & 2) {
-#pragma unroll
-              for (int z = 0; z < 4; ++z) {
-                lo[4 * i + z] = words[i].x ^ a_lo;
-                hi[4 * i + z] = words[i].y ^ b_hi;
-              }
-              if (z_keep(a_hi, b_lo)) sh.pad = 1;
-            } else {
-              dequant_word(words[i].x, a_lo, a_hi, lo + 4 * i);
-              dequant_word(words[i].y, b_lo, b_hi, hi + 4 * i);
-            }
+            unbias_word(words[i].x, lo + 4 * i);
+            unbias_word(words[i].y, hi + 4 * i);
           }
+          // scales[g].x = {slab A row r, slab A row r+8} of K32 group g; .y = same for slab B.
+          const uint32_t a0_lo = __byte_perm(scales[0].x, 0, 0x1010), a0_hi = __byte_perm(scales[0].x, 0, 0x3232);
+          const uint32_t a1_lo = __byte_perm(scales[1].x, 0, 0x1010), a1_hi = __byte_perm(scales[1].x, 0, 0x3232);
+          const uint32_t b0_lo = __byte_perm(scales[0].y, 0, 0x1010), b0_hi = __byte_perm(scales[0].y, 0, 0x3232);
+          const uint32_t b1_lo = __byte_perm(scales[1].y, 0, 0x1010), b1_hi = __byte_perm(scales[1].y, 0, 0x3232);
           CHORD_PROF_ADD(2, pt1);
           if (ok) {
             CHORD_PROF_T(pt3);
             ptx::tc_fence_after();
             const uint32_t a_addr = a_lane + slot.s * 32u;
-            ptx::tmem_st_16x128b_x8(a_addr, lo);
-            ptx::tmem_st_16x128b_x8(a_addr + (16u << 16), hi);
+            ptx::tmem_st_16x128b_x8_scaled(a_addr, lo, a0_lo, a0_hi, a1_lo, a1_hi);
+            ptx::tmem_st_16x128b_x8_scaled(a_addr + (16u << 16), hi, b0_lo, b0_hi, b1_lo, b1_hi);
             ptx::tmem_wait_st();
             ptx::tc_fence_before();
             __syncwarp();

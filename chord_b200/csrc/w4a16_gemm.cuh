@@ -375,6 +375,23 @@ __device__ __forceinline__ void dequant_word(uint32_t w, uint32_t scale_lo, uint
   out[3] = bf16x2_mul(bf16x2_sub(v3, kBias), scale_hi);  // rows r+8, K-half 1
 }
 
+// First half of dequant_word: the four BF16 pairs (code - 8), exact, in the same order;
+// the multiplication by the scales is left to tmem_st_16x128b_x8_scaled.
+__device__ __forceinline__ void unbias_word(uint32_t w, uint32_t* out) {
+  constexpr uint32_t kMask = 0x000F000Fu;
+  constexpr uint32_t kMagic = 0x43004300u;
+  constexpr uint32_t kBias = 0x43084308u;
+  uint32_t v0, v1, v2, v3;
+  asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(v0) : "r"(w), "r"(kMask), "r"(kMagic));
+  asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(v1) : "r"(w >> 4), "r"(kMask), "r"(kMagic));
+  asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(v2) : "r"(w >> 8), "r"(kMask), "r"(kMagic));
+  asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(v3) : "r"(w >> 12), "r"(kMask), "r"(kMagic));
+  out[0] = bf16x2_sub(v0, kBias);
+  out[2] = bf16x2_sub(v1, kBias);
+  out[1] = bf16x2_sub(v2, kBias);
+  out[3] = bf16x2_sub(v3, kBias);
+}
+
 // Ring position advanced without divisions (a lone issuing thread pays ~100
 // cycles for an integer division by a runtime value).
 struct StageCursor {
