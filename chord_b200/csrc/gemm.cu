@@ -205,28 +205,27 @@ int64_t decode_workspace_bytes(int grid, int mma_n) {
 
 int launch_decode(GemmParams p, const DeviceInfo& dev, const int32_t* packed, const void* scale,
                   int grid, cudaStream_t stream) {
-  // Shared memory: one ring per worker, as deep as fits next to the barriers and the
-  // epilogue buffers.  Two stages are being read by MMAs in flight and two more wait
-  // for their activation gather to be published, so fewer than six would stall.
+  // Shared memory: one ring of 128-wide K stages per worker, as deep as fits next to the
+  // barriers and the epilogue buffers (four stages for 16-token tiles, three for 32).
   const size_t fixed = sizeof(DecodeShared) + 1024;
   const size_t stage_bytes = decode_stage_bytes(p.mma_n);
   int stages = static_cast<int>((static_cast<size_t>(dev.max_smem_optin) - fixed) / kDecWorkers / stage_bytes);
   if (stages > kDecMaxStages) stages = kDecMaxStages;
   const int cap = options().max_stages;
-  if (cap > 0 && stages > cap) stages = cap < 4 ? 4 : cap;
-  CHORD_REQUIRE(stages >= 4, "internal: decode ring too shallow (%d stages)", stages);
+  if (cap > 0 && stages > cap) stages = cap < 3 ? 3 : cap;
+  CHORD_REQUIRE(stages >= 3, "internal: decode ring too shallow (%d stages)", stages);
   p.w_stages = stages;
   p.x_stages = stages;
   CUtensorMap tm_w, tm_s;
   if (int rc = make_map_2d(&tm_w, packed, CU_TENSOR_MAP_DATA_TYPE_INT32, 4,
                            static_cast<uint64_t>(p.n) * 2,
-                           static_cast<uint64_t>(p.num_experts) * (p.k / 16), 256, kDecStepK / 16,
+                           static_cast<uint64_t>(p.num_experts) * (p.k / 16), 256, kDecStageK / 16,
                            CU_TENSOR_MAP_SWIZZLE_NONE))
     return rc;
   if (int rc = make_map_2d(&tm_s, scale, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
                            static_cast<uint64_t>(p.n),
                            static_cast<uint64_t>(p.num_experts) * (p.k / 32), kBlockN,
-                           kDecStepK / 32, CU_TENSOR_MAP_SWIZZLE_NONE))
+                           kDecStageK / 32, CU_TENSOR_MAP_SWIZZLE_NONE))
     return rc;
   const size_t smem = kDecWorkers * static_cast<size_t>(stages) * stage_bytes + fixed;
   static std::once_flag flags[64];

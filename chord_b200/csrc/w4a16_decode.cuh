@@ -33,11 +33,12 @@
 
 namespace chord {
 
-constexpr int kDecStepK = 64;                        // K elements per step
-constexpr int kDecWBytes = (kDecStepK / 16) * 1024;  // packed weights per step
-constexpr int kDecSBytes = (kDecStepK / 32) * 256;   // scales per step
-constexpr int kDecWSBytes = 5120;                    // weights + scales, padded to keep stages 1024-aligned
-constexpr int kDecMaxStages = 12;
+constexpr int kDecStepK = 64;                        // K elements per step (one operand slot, four MMAs)
+constexpr int kDecStageK = 2 * kDecStepK;            // K elements per ring stage (two steps)
+constexpr int kDecWBytes = (kDecStageK / 16) * 1024;  // packed weights per stage
+constexpr int kDecSBytes = (kDecStageK / 32) * 256;   // scales per stage
+constexpr int kDecWSBytes = kDecWBytes + kDecSBytes;  // 9 KB: keeps stages 1024-aligned
+constexpr int kDecMaxStages = 6;
 constexpr int kDecMaxTokens = 32;
 constexpr int kDecWorkers = 4;                       // warpgroups per CTA
 constexpr int kDecThreads = 32 * (2 * kDecWorkers + 4 * kDecWorkers);  // feeders, issuers, workers
@@ -52,7 +53,7 @@ struct __align__(16) DecodeWorkerShared {
   uint64_t afree[kDecSlots];      // the MMAs reading the operand slot have completed (1 commit)
   uint64_t afull[kDecSlots];      // operand slot stored by the four warps (4 arrivals)
   int32_t out_row[kDecMaxTokens];
-  __align__(16) __nv_bfloat16 stage[4][16][32];  // epilogue transpose buffers, one per warp
+  __align__(16) __nv_bfloat16 stage[4][8][32];   // epilogue transpose buffers, one per warp
 };
 
 struct __align__(16) DecodeShared {
@@ -66,9 +67,10 @@ struct __align__(16) DecodeShared {
 
 __device__ __forceinline__ bool z_keep(uint32_t a, uint32_t b) { return a == 0x13572468u && b == 0x24681357u; }
 
-// Bytes of one ring stage: activation rows first (1024-aligned for the swizzle).
+// Bytes of one ring stage: the activation rows of both 64-wide K halves first
+// (1024-aligned for the swizzle), then packed weights and scales.
 __host__ __device__ inline uint32_t decode_stage_bytes(int mma_n) {
-  return static_cast<uint32_t>(mma_n) * 128u + kDecWSBytes;
+  return static_cast<uint32_t>(mma_n) * 256u + kDecWSBytes;
 }
 
 // decode_tile() of the general kernel without its contiguous branch (not served here),
@@ -156,14 +158,16 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
   const uint32_t raw_addr = ptx::smem_u32(smem_raw);
   uint8_t* smem = smem_raw + ((1024u - (raw_addr & 1023u)) & 1023u);
   const uint32_t stages = static_cast<uint32_t>(p.w_stages);
-  const uint32_t x_bytes = static_cast<uint32_t>(p.mma_n) * 128u;
+  const uint32_t x_half_bytes = static_cast<uint32_t>(p.mma_n) * 128u;  // one K half of the activation rows
+  const uint32_t x_bytes = 2u * x_half_bytes;
   const uint32_t stage_bytes = x_bytes + kDecWSBytes;
   const uint32_t worker_bytes = stages * stage_bytes;
   DecodeShared& sh = *reinterpret_cast<DecodeShared*>(smem + kDecWorkers * worker_bytes);
 
   const uint32_t warp = threadIdx.x >> 5;
   const uint32_t lane = threadIdx.x & 31;
-  const int32_t k_steps = p.k / kDecStepK;
+  const int32_t k_steps = (p.k + kDecStageK - 1) / kDecStageK;  // ring stages per tile
+  const bool k_tail_half = (p.k % kDecStageK) != 0;             // last stage: first K half only
 
   if (threadIdx.x == 0) {
     ptx::prefetch_tensormap(&tm_w);
@@ -241,9 +245,9 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
     // The two halves of a stage have different lifetimes: the packed weights and scales
     // are free again as soon as the worker's warps hold them in registers, the
     // activation rows only when the MMAs that read them have completed.  The feeder
-    // therefore walks the worker's step sequence twice: `wsm` (lane 0: two TMA boxes per
-    // step) runs stages - 2 steps ahead of `xsm` (all lanes: cp.async gather, lane l
-    // fetching the 16-byte piece l % 8 of rows l / 8 + 4 b, b < mma_n / 4).  In steady
+    // therefore walks the worker's stage sequence twice: `wsm` (lane 0: two TMA boxes per
+    // stage) runs stages - 2 stages ahead of `xsm` (all lanes: cp.async gather, lane l
+    // fetching the 16-byte piece l % 8 of rows l / 8 + 4 b, b < mma_n / 4, of both K halves).  In steady
     // state both waits below are over when they are reached, and the weight stream stays
     // a full ring ahead of the workers.
     const uint32_t piece = lane & 7u;
@@ -275,8 +279,8 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
           break;
         }
         if (first) {
-          w_row = wsm.t.expert * (p.k / 16) + wsm.kb * (kDecStepK / 16);
-          s_row = wsm.t.expert * (p.k / 32) + wsm.kb * (kDecStepK / 32);
+          w_row = wsm.t.expert * (p.k / 16) + wsm.kb * (kDecStageK / 16);
+          s_row = wsm.t.expert * (p.k / 32) + wsm.kb * (kDecStageK / 32);
           w_col = wsm.t.n0;
         }
         CHORD_PROF_T(ft0);
@@ -295,8 +299,8 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
         }
         __syncwarp();
         CHORD_PROF_ADD(2, ft1);
-        w_row += kDecStepK / 16;
-        s_row += kDecStepK / 32;
+        w_row += kDecStageK / 16;
+        s_row += kDecStageK / 32;
         wcur.advance(stages);
         ++w_ahead;
       }
@@ -316,7 +320,7 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
           x_off[b] = off;
           if (__ballot_sync(0xffffffffu, off >= 0) != 0) active |= 1u << b;
         }
-        src = p.x + xsm.kb * kDecStepK + piece * 8;
+        src = p.x + xsm.kb * kDecStageK + piece * 8;
       }
       CHORD_PROF_T(ft2);
       if (!ptx::mbar_wait_warp(xempty0 + xcur.s * 8u, xcur.ph ^ 1u, abort_flag)) {
@@ -326,10 +330,13 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
       CHORD_PROF_ADD(3, ft2);
       CHORD_PROF_T(ft3);
       const uint32_t xs = ring + xcur.s * stage_bytes;
+      const bool second_half = !(k_tail_half && xsm.kb == k_steps - 1);
 #pragma unroll
       for (int b = 0; b < 8; ++b) {
         if (!(DEC_ABLATE & 8) && ((active >> b) & 1u) && x_off[b] >= 0) {
-          ptx::cp_async_16(xs + dst_off[b & 1] + (b >> 1) * 1024u, src + x_off[b], true);
+          const uint32_t dst = xs + dst_off[b & 1] + (b >> 1) * 1024u;
+          ptx::cp_async_16(dst, src + x_off[b], true);
+          if (second_half) ptx::cp_async_16(dst + x_half_bytes, src + x_off[b] + kDecStepK, true);
         }
       }
       ptx::cp_async_commit();
@@ -343,7 +350,7 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
         xdone.advance(stages);
       }
       x_pending = true;
-      src += kDecStepK;
+      src += kDecStageK;
       xcur.advance(stages);
       --w_ahead;
       CHORD_PROF_ADD(4, ft3);
@@ -363,7 +370,9 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
   } else if (warp < 8) {
     // ------------------------------------------------- MMA issuer of worker `warp - 4` --
     // One tcgen05.mma costs its issuing thread some tens of cycles whatever its size, and
-    // a 64-wide step needs four: kept off the warps that dequantise.
+    // a 64-wide step needs four: kept off the warps that dequantise.  A stage carries two
+    // steps (one operand slot each); the activation half of the stage goes back to the
+    // feeder with the second one.
     const uint32_t d_tm = tmem_base + col0 + kDecDCol;
     StageCursor cur, slot;
     bool ok = true;
@@ -372,31 +381,35 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
       if (!t.valid) continue;
       const uint32_t idesc = ptx::idesc_bf16_f32(kBlockN, static_cast<uint32_t>(t.mma_n));
       uint32_t acc = 0;
-      for (int32_t kb = seg.kb; kb < seg.ke; ++kb) {
+      for (int32_t kb = seg.kb; ok && kb < seg.ke; ++kb) {
         // No wait is needed for the accumulator: the first store of a segment follows
         // its warp's share of the previous segment's epilogue.
-        if (!ptx::mbar_wait_warp(afull0 + slot.s * 8u, slot.ph, abort_flag) ||
-            !ptx::mbar_wait_warp(xfull0 + cur.s * 8u, cur.ph, abort_flag)) {
-          ok = false;
-          break;
-        }
-        ptx::tc_fence_after();
-        if (lane == 0) {
-          const uint64_t xdesc = ptx::smem_desc_k_sw128(ring + cur.s * stage_bytes);
-          const uint32_t a_tm = tmem_base + col0 + slot.s * 32u;
-          if (!(DEC_ABLATE & 1)) {
-            ptx::mma_ts(d_tm, a_tm, xdesc, idesc, acc);
-            ptx::mma_ts(d_tm, a_tm + 8, xdesc + 2, idesc, 1);
-            ptx::mma_ts(d_tm, a_tm + 16, xdesc + 4, idesc, 1);
-            ptx::mma_ts(d_tm, a_tm + 24, xdesc + 6, idesc, 1);
+        const int32_t halves = (k_tail_half && kb == k_steps - 1) ? 1 : 2;
+        const uint32_t stage = ring + cur.s * stage_bytes;
+        for (int32_t h = 0; h < halves; ++h) {
+          if (!ptx::mbar_wait_warp(afull0 + slot.s * 8u, slot.ph, abort_flag) ||
+              (h == 0 && !ptx::mbar_wait_warp(xfull0 + cur.s * 8u, cur.ph, abort_flag))) {
+            ok = false;
+            break;
           }
-          ptx::mma_commit(xempty0 + cur.s * 8u);
-          ptx::mma_commit(afree0 + slot.s * 8u);
+          ptx::tc_fence_after();
+          if (lane == 0) {
+            const uint64_t xdesc = ptx::smem_desc_k_sw128(stage + static_cast<uint32_t>(h) * x_half_bytes);
+            const uint32_t a_tm = tmem_base + col0 + slot.s * 32u;
+            if (!(DEC_ABLATE & 1)) {
+              ptx::mma_ts(d_tm, a_tm, xdesc, idesc, acc);
+              ptx::mma_ts(d_tm, a_tm + 8, xdesc + 2, idesc, 1);
+              ptx::mma_ts(d_tm, a_tm + 16, xdesc + 4, idesc, 1);
+              ptx::mma_ts(d_tm, a_tm + 24, xdesc + 6, idesc, 1);
+            }
+            if (h == halves - 1) ptx::mma_commit(xempty0 + cur.s * 8u);
+            ptx::mma_commit(afree0 + slot.s * 8u);
+          }
+          __syncwarp();
+          acc = 1;
+          slot.advance(kDecSlots);
         }
-        __syncwarp();
-        acc = 1;
         cur.advance(stages);
-        slot.advance(kDecSlots);
       }
     }
     if (!ok && lane == 0) {
@@ -433,20 +446,37 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
       uint32_t last_bar = 0, last_ph = 0;
       for (int32_t j = 0; j < n_steps; ++j) {
         const uint32_t st = ring + cur.s * stage_bytes;
+        const bool two_halves = !(k_tail_half && seg.kb + j == k_steps - 1);
         CHORD_PROF_T(pt0);
         if (ok) ok = ptx::mbar_wait_warp(wfull0 + cur.s * 8u, cur.ph, abort_flag);
         CHORD_PROF_ADD(1, pt0);
-        if (ok) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          if (!ok || (h == 1 && !two_halves)) continue;
           CHORD_PROF_T(pt1);
+          // K half h of the stage: four K16 rows of packed words, two K32 groups of scales.
           uint2 words[4], scales[2];
-          words[0] = ptx::lds64<0>(st + w_off);
-          words[1] = ptx::lds64<1024>(st + w_off);
-          words[2] = ptx::lds64<2048>(st + w_off);
-          words[3] = ptx::lds64<3072>(st + w_off);
-          scales[0] = ptx::lds64<0>(st + s_off);
-          scales[1] = ptx::lds64<256>(st + s_off);
-          __syncwarp();
-          if (lane == 0) ptx::mbar_arrive(wempty0 + cur.s * 8u);
+          if (h == 0) {
+            words[0] = ptx::lds64<0>(st + w_off);
+            words[1] = ptx::lds64<1024>(st + w_off);
+            words[2] = ptx::lds64<2048>(st + w_off);
+            words[3] = ptx::lds64<3072>(st + w_off);
+            scales[0] = ptx::lds64<0>(st + s_off);
+            scales[1] = ptx::lds64<256>(st + s_off);
+          } else {
+            words[0] = ptx::lds64<4096>(st + w_off);
+            words[1] = ptx::lds64<5120>(st + w_off);
+            words[2] = ptx::lds64<6144>(st + w_off);
+            words[3] = ptx::lds64<7168>(st + w_off);
+            scales[0] = ptx::lds64<512>(st + s_off);
+            scales[1] = ptx::lds64<768>(st + s_off);
+          }
+          if (h == 1 || !two_halves) {
+            // The weight half of the stage goes back to the feeder as soon as its last
+            // words are in registers.
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(wempty0 + cur.s * 8u);
+          }
           // The operand slot is free once the MMAs of its previous use have completed.
           // Waited for here, before the dequantised values exist: with thirty-two of them
           // live, the wait's out-of-line slow path costs a register shuffle.
@@ -483,10 +513,10 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
           }
           last_bar = afree;
           last_ph = slot.ph;
+          slot.advance(kDecSlots);
         }
         if (!ok) sh.abort_flag = 1;
         cur.advance(stages);
-        slot.advance(kDecSlots);
       }
       // ---- end of the segment: wait for its last MMAs, then drain the accumulator.
       {
@@ -529,22 +559,22 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
                 for (int i = 0; i < 16; ++i) accv[i] += __ldcg(part + i * kBlockN);
               }
             }
-            // Transpose through shared memory so that global stores are 16 bytes wide.
+            // Transpose through shared memory so that global stores are 16 bytes wide: eight
+            // tokens at a time (32 weight rows x 8 tokens = one 16-byte piece per lane).
             __nv_bfloat16* stage = &ws.stage[q][0][0];
 #pragma unroll
-            for (int i = 0; i < 16; ++i) stage[i * 32 + lane] = __float2bfloat16_rn(accv[i]);
-            __syncwarp();
+            for (int half = 0; half < 2; ++half) {
 #pragma unroll
-            for (int i = 0; i < 2; ++i) {
-              const uint32_t idx = lane + 32 * i;
-              const uint32_t tj = idx >> 2, pc = idx & 3;
-              const int32_t row = ws.out_row[c0 + tj];
+              for (int i = 0; i < 8; ++i) stage[i * 32 + lane] = __float2bfloat16_rn(accv[8 * half + i]);
+              __syncwarp();
+              const uint32_t tj = lane >> 2, pc = lane & 3;
+              const int32_t row = ws.out_row[c0 + 8 * half + tj];
               const uint4 val = *reinterpret_cast<const uint4*>(stage + tj * 32 + pc * 8);
               if (row >= 0) {
                 *reinterpret_cast<uint4*>(out_tile + static_cast<size_t>(row) * p.n + pc * 8) = val;
               }
+              __syncwarp();
             }
-            __syncwarp();
           }
           ptx::tc_fence_before();
           if (seg.type == kSegContrib) __threadfence();
