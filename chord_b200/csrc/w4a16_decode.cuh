@@ -226,7 +226,9 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
   const int32_t tiles = sh.m_blocks * (p.n / kBlockN);
   // warps 0-3 feed, warps 4-7 issue the MMAs, warps 8-23 are the four workers
   const uint32_t wk = warp < 8 ? (warp & 3u) : (warp - 8) >> 2;
-  const int32_t worker_id = static_cast<int32_t>(blockIdx.x) * kDecWorkers + static_cast<int32_t>(wk);
+  // Worker ids interleave the CTAs (worker w of CTA c is c + w * grid), so that a launch
+  // with fewer slices than workers spreads them over all SMs first.
+  const int32_t worker_id = static_cast<int32_t>(wk * gridDim.x + blockIdx.x);
   SegmentIterator iter;
   iter.init(tiles, k_steps, static_cast<int32_t>(gridDim.x) * kDecWorkers, worker_id);
   Segment seg;

@@ -203,7 +203,10 @@ struct SegmentIterator {
     dp_tiles = dp_waves * grid;
     wave = 0;
     units = static_cast<int64_t>(sk_tiles) * ki;
-    geff = units < grid ? static_cast<int32_t>(units) : grid;
+    // No slice shorter than eight k-blocks (unless the whole tail is): a finer split costs
+    // more in partial sums and per-slice set-up than the extra parallelism returns.
+    const int64_t slices = units / 8 > 0 ? units / 8 : (units > 0 ? 1 : 0);
+    geff = slices < grid ? static_cast<int32_t>(slices) : grid;
     if (cta < geff) {
       u0 = cta * units / geff;
       u1 = (cta + 1) * units / geff;
