@@ -52,7 +52,6 @@ struct __align__(16) DecodeWorkerShared {
   uint64_t xempty[kDecMaxStages];  // the MMAs reading them have completed (1 commit)
   uint64_t afree[kDecSlots];      // the MMAs reading the operand slot have completed (1 commit)
   uint64_t afull[kDecSlots];      // operand slot stored by the four warps (4 arrivals)
-  int32_t out_row[kDecMaxTokens];
   __align__(16) __nv_bfloat16 stage[4][8][32];   // epilogue transpose buffers, one per warp
 };
 
@@ -149,6 +148,87 @@ struct StepStream {
     return false;
   }
 };
+
+// Accumulator -> BF16 -> global for one warp's 32 weight rows of one segment.  Lane l
+// holds the output row of token slot l (`rows`).  A whole tile needs nothing from the
+// worker's other three warps; a stream-K slice does (lock, partials), and only then do
+// the four warps meet at named barriers.  Kept out of line: it runs once per tile, and
+// inlined into the dequantisation loop it took registers from that loop.
+__device__ __noinline__ void decode_drain(uint32_t d_addr, __nv_bfloat16* out_tile, int32_t ldn,
+                                          int32_t rows, int32_t mma_n, int32_t seg_type, int32_t seg_peer,
+                                          float* workspace, size_t ws_slot, int32_t worker_id,
+                                          int32_t* locks, int32_t* status, __nv_bfloat16* stage,
+                                          uint32_t bar_id, uint32_t wt, bool ok) {
+  const uint32_t lane = threadIdx.x & 31u;
+  const uint32_t q = (threadIdx.x >> 5) & 3u;
+  ptx::tc_fence_after();
+  const bool shared_tile = seg_type != kSegFull;
+  if (shared_tile) {
+    if (ok && seg_type == kSegOwner && wt == 0) {
+      const int* lock = locks + worker_id;
+      bool lock_ok = false;
+      for (uint32_t spin = 0; spin < (1u << 22); ++spin) {
+        if (ptx::ld_acquire(lock) >= seg_peer) {
+          lock_ok = true;
+          break;
+        }
+        __nanosleep(64);
+      }
+      if (!lock_ok && status) atomicOr(status, kStatusLockTimeout);
+    }
+    ptx::named_bar_sync(bar_id, 128);  // lock observed
+  }
+  if (ok) {
+    for (int32_t c0 = 0; c0 < mma_n; c0 += 16) {
+      uint32_t v[16];
+      ptx::tmem_ld_32x32b_x16(d_addr + c0, v);
+      ptx::tmem_wait_ld();
+      float accv[16];
+#pragma unroll
+      for (int i = 0; i < 16; ++i) accv[i] = __uint_as_float(v[i]);
+      if (seg_type == kSegContrib) {
+        float* dst = workspace + worker_id * ws_slot + static_cast<size_t>(c0) * kBlockN + q * 32 + lane;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) __stcg(dst + i * kBlockN, accv[i]);
+        continue;
+      }
+      if (seg_type == kSegOwner) {
+        for (int32_t peer = 1; peer <= seg_peer; ++peer) {
+          const float* part = workspace + (worker_id + peer) * ws_slot + static_cast<size_t>(c0) * kBlockN +
+                              q * 32 + lane;
+#pragma unroll
+          for (int i = 0; i < 16; ++i) accv[i] += __ldcg(part + i * kBlockN);
+        }
+      }
+      // Transpose through shared memory so that global stores are 16 bytes wide: eight
+      // tokens at a time (32 weight rows x 8 tokens = one 16-byte piece per lane).
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) stage[i * 32 + lane] = __float2bfloat16_rn(accv[8 * half + i]);
+        __syncwarp();
+        const uint32_t tj = lane >> 2, pc = lane & 3;
+        const int32_t row = __shfl_sync(0xffffffffu, rows, c0 + 8 * half + static_cast<int32_t>(tj));
+        const uint4 val = *reinterpret_cast<const uint4*>(stage + tj * 32 + pc * 8);
+        if (row >= 0) {
+          *reinterpret_cast<uint4*>(out_tile + static_cast<size_t>(row) * ldn + pc * 8) = val;
+        }
+        __syncwarp();
+      }
+    }
+    ptx::tc_fence_before();
+    if (seg_type == kSegContrib) __threadfence();
+  }
+  if (shared_tile) {
+    ptx::named_bar_sync(bar_id, 128);  // all four warps' partials are written / read
+    if (wt == 0) {
+      // The stream-K handshake is completed even after a failure, so that no other
+      // worker spins on a lock that would never move; the status word tells the host.
+      if (seg_type == kSegContrib) ptx::red_release_add(locks + seg_peer, 1);
+      else locks[worker_id] = 0;
+    }
+  }
+}
 
 __global__ void __launch_bounds__(kDecThreads, 1)
 w4a16_decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_s,
@@ -440,11 +520,17 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
     CHORD_PROF_INIT();
     const size_t ws_slot = static_cast<size_t>(kBlockN) * p.mma_n;
 
+    auto drain = [&](const Segment& sg, int32_t rows, int32_t n0, uint32_t dcol, int32_t mma_n) {
+      decode_drain(tmem_base + ((q * 32u) << 16) + dcol, p.out + n0 + q * 32, p.n, rows, mma_n, sg.type,
+                   sg.peer, p.workspace, ws_slot, worker_id, p.locks, p.status, &ws.stage[q][0][0], bar_id,
+                   wt, ok);
+    };
     while (iter.next(seg)) {
       const TileInfo t = decode_tile_small(p, sh.group_prefix, seg.tile);
       if (!t.valid) continue;
       const int32_t n_steps = seg.ke - seg.kb;
-      if (wt < static_cast<uint32_t>(t.mma_n)) ws.out_row[wt] = out_row_of(p, t, static_cast<int32_t>(wt));
+      // Output row of token slot `lane`: loaded now, used in the epilogue.
+      const int32_t my_out_row = out_row_of(p, t, static_cast<int32_t>(lane));
       uint32_t last_bar = 0, last_ph = 0;
       for (int32_t j = 0; j < n_steps; ++j) {
         const uint32_t st = ring + cur.s * stage_bytes;
@@ -521,74 +607,12 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
         cur.advance(stages);
       }
       // ---- end of the segment: wait for its last MMAs, then drain the accumulator.
-      {
-        if (ok) ok = ptx::mbar_wait_warp(last_bar, last_ph, abort_flag);
-        ptx::tc_fence_after();
-        if (ok && seg.type == kSegOwner && wt == 0) {
-          const int* lock = p.locks + worker_id;
-          bool lock_ok = false;
-          for (uint32_t spin = 0; spin < (1u << 22); ++spin) {
-            if (ptx::ld_acquire(lock) >= seg.peer) {
-              lock_ok = true;
-              break;
-            }
-            __nanosleep(64);
-          }
-          if (!lock_ok && p.status) atomicOr(p.status, kStatusLockTimeout);
-        }
-        ptx::named_bar_sync(bar_id, 128);  // out_row written, lock observed
-        if (ok) {
-          const uint32_t d_addr = tmem_base + ((q * 32u) << 16) + col0 + kDecDCol;
-          __nv_bfloat16* out_tile = p.out + t.n0 + q * 32;
-          for (int32_t c0 = 0; c0 < t.mma_n; c0 += 16) {
-            uint32_t v[16];
-            ptx::tmem_ld_32x32b_x16(d_addr + c0, v);
-            ptx::tmem_wait_ld();
-            float accv[16];
-#pragma unroll
-            for (int i = 0; i < 16; ++i) accv[i] = __uint_as_float(v[i]);
-            if (seg.type == kSegContrib) {
-              float* dst = p.workspace + worker_id * ws_slot + static_cast<size_t>(c0) * kBlockN + q * 32 + lane;
-#pragma unroll
-              for (int i = 0; i < 16; ++i) __stcg(dst + i * kBlockN, accv[i]);
-              continue;
-            }
-            if (seg.type == kSegOwner) {
-              for (int32_t peer = 1; peer <= seg.peer; ++peer) {
-                const float* part = p.workspace + (worker_id + peer) * ws_slot +
-                                    static_cast<size_t>(c0) * kBlockN + q * 32 + lane;
-#pragma unroll
-                for (int i = 0; i < 16; ++i) accv[i] += __ldcg(part + i * kBlockN);
-              }
-            }
-            // Transpose through shared memory so that global stores are 16 bytes wide: eight
-            // tokens at a time (32 weight rows x 8 tokens = one 16-byte piece per lane).
-            __nv_bfloat16* stage = &ws.stage[q][0][0];
-#pragma unroll
-            for (int half = 0; half < 2; ++half) {
-#pragma unroll
-              for (int i = 0; i < 8; ++i) stage[i * 32 + lane] = __float2bfloat16_rn(accv[8 * half + i]);
-              __syncwarp();
-              const uint32_t tj = lane >> 2, pc = lane & 3;
-              const int32_t row = ws.out_row[c0 + 8 * half + tj];
-              const uint4 val = *reinterpret_cast<const uint4*>(stage + tj * 32 + pc * 8);
-              if (row >= 0) {
-                *reinterpret_cast<uint4*>(out_tile + static_cast<size_t>(row) * p.n + pc * 8) = val;
-              }
-              __syncwarp();
-            }
-          }
-          ptx::tc_fence_before();
-          if (seg.type == kSegContrib) __threadfence();
-        }
-        ptx::named_bar_sync(bar_id, 128);  // accumulator and out_row are free again
-        if (wt == 0) {
-          // The stream-K handshake is completed even after a failure, so that no other
-          // worker spins on a lock that would never move; the status word tells the host.
-          if (seg.type == kSegContrib) ptx::red_release_add(p.locks + seg.peer, 1);
-          else if (seg.type == kSegOwner) p.locks[worker_id] = 0;
-        }
-      }
+      CHORD_PROF_T(pe0);
+      if (ok) ok = ptx::mbar_wait_warp(last_bar, last_ph, abort_flag);
+      CHORD_PROF_ADD(6, pe0);
+      CHORD_PROF_T(pe1);
+      drain(seg, my_out_row, t.n0, col0 + kDecDCol, t.mma_n);
+      CHORD_PROF_ADD(7, pe1);
     }
     if (wk == 0 && q < 2) CHORD_PROF_FLUSH(q);
     if (!ok && lane == 0) {
