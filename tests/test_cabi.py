@@ -113,6 +113,29 @@ def test_schedule_owner_never_waits_on_an_earlier_cta(native_lib):
             assert all(kind == 0 for kind in before)
 
 
+@pytest.mark.parametrize("tiles,k,grid", [(32, 7168, 592), (56, 2048, 592), (1, 7168, 592), (3, 512, 148),
+                                          (352, 7168, 592), (1088, 7168, 592)])
+def test_schedule_slices_are_not_slivers(native_lib, tiles, k, grid):
+    """The stream-K tail is cut into slices of at least eight k-blocks (fewer only if the
+    whole tail is shorter), also when there are far more workers than work: the decode
+    kernel schedules four workers per SM."""
+    k_iters = (k + 127) // 128
+    lengths, busy = [], 0
+    for cta in range(grid):
+        segs = _segments(native_lib, tiles, k, grid, cta)
+        partial = [(int(ke - kb)) for _, kb, ke, kind, _ in segs if kind != 0]
+        whole = [1 for _, _, _, kind, _ in segs if kind == 0]
+        if len(segs):
+            busy += 1
+        work = sum(int(ke - kb) for _, kb, ke, _, _ in segs)
+        if work and partial:
+            lengths.append(work)
+    tail_units = (tiles % grid if tiles >= grid else tiles) * k_iters
+    if lengths:
+        assert min(lengths) >= min(8, tail_units)
+    assert busy <= max(1, grid)
+
+
 def test_schedule_rejects_bad_queries(native_lib):
     assert native_lib.chord_b200_schedule_segments(10, 100, 148, 0, None, 0) < 0
     assert native_lib.chord_b200_schedule_segments(10, 128, 148, 148, None, 0) < 0
