@@ -366,7 +366,7 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
           w_col = wsm.t.n0;
         }
         CHORD_PROF_T(ft0);
-        if (!ptx::mbar_wait_warp<false>(wempty0 + wcur.s * 8u, wcur.ph ^ 1u, abort_flag)) {
+        if (!ptx::mbar_wait_parked(wempty0 + wcur.s * 8u, wcur.ph ^ 1u, abort_flag)) {
           ok = false;
           break;
         }
@@ -405,7 +405,7 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
         src = p.x + xsm.kb * kDecStageK + piece * 8;
       }
       CHORD_PROF_T(ft2);
-      if (!ptx::mbar_wait_warp<false>(xempty0 + xcur.s * 8u, xcur.ph ^ 1u, abort_flag)) {
+      if (!ptx::mbar_wait_parked(xempty0 + xcur.s * 8u, xcur.ph ^ 1u, abort_flag)) {
         ok = false;
         break;
       }
@@ -469,8 +469,8 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
         const int32_t halves = (k_tail_half && kb == k_steps - 1) ? 1 : 2;
         const uint32_t stage = ring + cur.s * stage_bytes;
         for (int32_t h = 0; h < halves; ++h) {
-          if (!ptx::mbar_wait_warp<false>(afull0 + slot.s * 8u, slot.ph, abort_flag) ||
-              (h == 0 && !ptx::mbar_wait_warp<false>(xfull0 + cur.s * 8u, cur.ph, abort_flag))) {
+          if (!ptx::mbar_wait_parked(afull0 + slot.s * 8u, slot.ph, abort_flag) ||
+              (h == 0 && !ptx::mbar_wait_parked(xfull0 + cur.s * 8u, cur.ph, abort_flag))) {
             ok = false;
             break;
           }
@@ -536,7 +536,7 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
         const uint32_t st = ring + cur.s * stage_bytes;
         const bool two_halves = !(k_tail_half && seg.kb + j == k_steps - 1);
         CHORD_PROF_T(pt0);
-        if (ok) ok = ptx::mbar_wait_warp<false>(wfull0 + cur.s * 8u, cur.ph, abort_flag);
+        if (ok) ok = ptx::mbar_wait_parked(wfull0 + cur.s * 8u, cur.ph, abort_flag);
         CHORD_PROF_ADD(1, pt0);
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
@@ -570,7 +570,7 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
           // live, the wait's out-of-line slow path costs a register shuffle.
           CHORD_PROF_T(pt2);
           const uint32_t afree = afree0 + slot.s * 8u;
-          ok = ptx::mbar_wait_warp<false>(afree, slot.ph ^ 1u, abort_flag);
+          ok = ptx::mbar_wait_parked(afree, slot.ph ^ 1u, abort_flag);
           CHORD_PROF_ADD(3, pt2);
           uint32_t lo[16], hi[16];
 #pragma unroll
@@ -608,7 +608,7 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
       }
       // ---- end of the segment: wait for its last MMAs, then drain the accumulator.
       CHORD_PROF_T(pe0);
-      if (ok) ok = ptx::mbar_wait_warp<false>(last_bar, last_ph, abort_flag);
+      if (ok) ok = ptx::mbar_wait_parked(last_bar, last_ph, abort_flag);
       CHORD_PROF_ADD(6, pe0);
       CHORD_PROF_T(pe1);
       drain(seg, my_out_row, t.n0, col0 + kDecDCol, t.mma_n);
