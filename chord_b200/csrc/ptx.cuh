@@ -55,6 +55,19 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 
+// Arrival by lane 0 of a converged warp, as one predicated instruction: written as
+// `if (lane == 0) mbar_arrive(bar)` it costs a divergent branch with its convergence
+// barrier around a single instruction, several times per pipeline step.
+__device__ __forceinline__ void mbar_arrive_lane0(uint32_t bar, uint32_t lane) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.eq.u32 p, %1, 0;\n\t"
+      "@p mbarrier.arrive.shared::cta.b64 _, [%0];\n\t"
+      "}\n" ::"r"(bar), "r"(lane)
+      : "memory");
+}
+
 __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
                : "memory");

@@ -563,7 +563,7 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
             // The weight half of the stage goes back to the feeder as soon as its last
             // words are in registers.
             __syncwarp();
-            if (lane == 0) ptx::mbar_arrive(wempty0 + cur.s * 8u);
+            ptx::mbar_arrive_lane0(wempty0 + cur.s * 8u, lane);
           }
           // The operand slot is free once the MMAs of its previous use have completed.
           // Waited for here, before the dequantised values exist: with thirty-two of them
@@ -595,8 +595,7 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
             __syncwarp();
             CHORD_PROF_ADD(4, pt3);
             CHORD_PROF_T(pt4);
-            if (lane == 0) ptx::mbar_arrive(afull0 + slot.s * 8u);
-            __syncwarp();
+            ptx::mbar_arrive_lane0(afull0 + slot.s * 8u, lane);
             CHORD_PROF_ADD(5, pt4);
           }
           last_bar = afree;
