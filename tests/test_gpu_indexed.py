@@ -291,3 +291,51 @@ def test_argument_checks(device):
         chord_b200.indexed(x, w, bad, e, p, 1, block_m=8, validate_routing=True)
     out = chord_b200.indexed(x, w, s, e, p, 1, block_m=8, validate_routing=True)  # locks=None is fine
     assert out.shape == (8, 128)
+
+
+def test_decode_step_replays_from_a_cuda_graph(device):
+    """gate_up -> SiLU*mul -> down captured once and replayed: the launches allocate only
+    from torch's (graph-pool aware) caching allocator and never synchronise, so a decode
+    loop can run them from a CUDA graph (reference: tests/test_w4a16_indexed.py:1208-1259).
+    Replays on new activations must match eager launches bit for bit."""
+    import chord_b200
+    from chord_b200.indexed_gemm import status_word
+
+    case = make_indexed_case(num_experts=8, n=1024, k=512, m=64, top_k=2, block_m=16, seed=41)
+    codes2, scale2 = make_checkpoint_weights(8, 512, 512, seed=42)
+    w13 = chord_b200.pack_w4a16(case["codes"].to(device), case["scale"].to(device))
+    w2 = chord_b200.pack_w4a16(codes2.to(device), scale2.to(device), packed=True)
+    routing = (case["sorted_ids"].to(device), case["expert_ids"].to(device),
+               case["num_tokens_padded"].to(device).reshape(1))
+    locks = torch.zeros(1024, dtype=torch.int32, device=device)
+    x = case["x"].to(device).clone()
+    gate_up = torch.zeros((128, 1024), dtype=torch.bfloat16, device=device)
+    hidden = torch.zeros((128, 512), dtype=torch.bfloat16, device=device)
+    out = torch.zeros((128, 512), dtype=torch.bfloat16, device=device)
+
+    def step():
+        chord_b200.indexed(x, w13, *routing, 2, locks=locks, outputs=gate_up, block_m=16)
+        chord_b200.silu_mul(gate_up, sorted_ids=routing[0], num_tokens_padded=routing[2], outputs=hidden)
+        chord_b200.indexed(hidden, w2, *routing, 1, locks=locks, outputs=out, block_m=16)
+
+    side = torch.cuda.Stream(device)
+    side.wait_stream(torch.cuda.current_stream(device))
+    with torch.cuda.stream(side):
+        for _ in range(2):
+            step()
+    torch.cuda.current_stream(device).wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        step()
+    g = torch.Generator().manual_seed(43)
+    for _ in range(3):
+        x.copy_(torch.randn(x.shape, generator=g).to(torch.bfloat16))
+        graph.replay()
+        torch.cuda.synchronize()
+        replayed = out.clone()
+        step()
+        torch.cuda.synchronize()
+        assert torch.equal(replayed.view(torch.int16), out.view(torch.int16))
+    assert int(status_word(device).item()) == 0
+    assert bool((locks == 0).all())
