@@ -503,7 +503,22 @@ def main():
             t = time_region(wl.step, args.steps, args.warmup, world, device)
             k_us = time_kernels(wl, max(args.steps, 5))
             gemm_bytes = wl.bytes_gate_up + wl.bytes_down
-            batches[str(b)] = {"us": t * 1e3, "gate_up_us": k_us[0], "silu_mul_us": k_us[1],
+            graph_us = None
+            try:
+                # the same step replayed from a CUDA graph (what a decode loop would do)
+                side = torch.cuda.Stream(device)
+                side.wait_stream(torch.cuda.current_stream(device))
+                with torch.cuda.stream(side):
+                    wl.step()
+                torch.cuda.current_stream(device).wait_stream(side)
+                torch.cuda.synchronize()
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph):
+                    wl.step()
+                graph_us = time_region(graph.replay, args.steps, args.warmup, world, device) * 1e3
+            except Exception:  # noqa: BLE001 - the eager number above stands on its own
+                graph_us = None
+            batches[str(b)] = {"us": t * 1e3, "graph_replay_us": graph_us, "gate_up_us": k_us[0], "silu_mul_us": k_us[1],
                                "down_us": k_us[2], "active_experts": wl.active, "routed_rows": wl.routed,
                                "block_m": wl.block_m,
                                "gemm_gbs": gemm_bytes / ((k_us[0] + k_us[2]) * 1e-6) / 1e9 if wl.active else None}
