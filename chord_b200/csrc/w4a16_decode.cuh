@@ -25,6 +25,8 @@
 //   * after the last step of a tile the same four warps run the epilogue.
 #pragma once
 
+#include <type_traits>
+
 #include "w4a16_gemm.cuh"
 
 #ifndef DEC_ABLATE
@@ -503,10 +505,10 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
     // ------------------------------------------------------------- worker warps --
     // Inside a segment the four warps run independently: each waits for the stage,
     // dequantises its 32 weight rows, waits for a free operand slot, stores, and tells
-    // the feeder.  They meet (named barrier) only around the epilogue.  Control flow is
-    // the same in all four whatever happens: a warp whose bounded wait gave up clears
-    // `ok` and skips the work, but still walks the loops and meets its siblings at every
-    // named barrier; the abort flag it raises makes the others' waits give up quickly.
+    // the issuer.  They meet (named barriers) only in the epilogue of a stream-K slice.
+    // A warp whose bounded wait gave up clears `ok`, raises the abort flag (so that the
+    // others' waits give up quickly too) and does no more work, but still walks the
+    // remaining segments and meets its siblings at those barriers.
     const uint32_t q = warp & 3;                          // TMEM lane quarter == 32 weight rows
     const uint32_t wt = threadIdx.x - (8 + 4 * wk) * 32;  // 0..127 inside the worker
     const uint32_t bar_id = 1 + wk;
@@ -532,83 +534,81 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
       // Output row of token slot `lane`: loaded now, used in the epilogue.
       const int32_t my_out_row = out_row_of(p, t, static_cast<int32_t>(lane));
       uint32_t last_bar = 0, last_ph = 0;
-      for (int32_t j = 0; j < n_steps; ++j) {
-        const uint32_t st = ring + cur.s * stage_bytes;
-        const bool two_halves = !(k_tail_half && seg.kb + j == k_steps - 1);
-        CHORD_PROF_T(pt0);
-        if (ok) ok = ptx::mbar_wait_parked(wfull0 + cur.s * 8u, cur.ph, abort_flag);
-        CHORD_PROF_ADD(1, pt0);
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          if (!ok || (h == 1 && !two_halves)) continue;
-          CHORD_PROF_T(pt1);
-          // K half h of the stage: four K16 rows of packed words, two K32 groups of scales.
-          uint2 words[4], scales[2];
-          if (h == 0) {
-            words[0] = ptx::lds64<0>(st + w_off);
-            words[1] = ptx::lds64<1024>(st + w_off);
-            words[2] = ptx::lds64<2048>(st + w_off);
-            words[3] = ptx::lds64<3072>(st + w_off);
-            scales[0] = ptx::lds64<0>(st + s_off);
-            scales[1] = ptx::lds64<256>(st + s_off);
-          } else {
-            words[0] = ptx::lds64<4096>(st + w_off);
-            words[1] = ptx::lds64<5120>(st + w_off);
-            words[2] = ptx::lds64<6144>(st + w_off);
-            words[3] = ptx::lds64<7168>(st + w_off);
-            scales[0] = ptx::lds64<512>(st + s_off);
-            scales[1] = ptx::lds64<768>(st + s_off);
-          }
-          if (h == 1 || !two_halves) {
-            // The weight half of the stage goes back to the feeder as soon as its last
-            // words are in registers.
-            __syncwarp();
-            ptx::mbar_arrive_lane0(wempty0 + cur.s * 8u, lane);
-          }
-          // The operand slot is free once the MMAs of its previous use have completed.
-          // Waited for here, before the dequantised values exist: with thirty-two of them
-          // live, the wait's out-of-line slow path costs a register shuffle.
-          CHORD_PROF_T(pt2);
-          const uint32_t afree = afree0 + slot.s * 8u;
-          ok = ptx::mbar_wait_parked(afree, slot.ph ^ 1u, abort_flag);
-          CHORD_PROF_ADD(3, pt2);
-          uint32_t lo[16], hi[16];
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            unbias_word(words[i].x, lo + 4 * i);
-            unbias_word(words[i].y, hi + 4 * i);
-          }
-          // scales[g].x = {slab A row r, slab A row r+8} of K32 group g; .y = same for slab B.
-          const uint32_t a0_lo = __byte_perm(scales[0].x, 0, 0x1010), a0_hi = __byte_perm(scales[0].x, 0, 0x3232);
-          const uint32_t a1_lo = __byte_perm(scales[1].x, 0, 0x1010), a1_hi = __byte_perm(scales[1].x, 0, 0x3232);
-          const uint32_t b0_lo = __byte_perm(scales[0].y, 0, 0x1010), b0_hi = __byte_perm(scales[0].y, 0, 0x3232);
-          const uint32_t b1_lo = __byte_perm(scales[1].y, 0, 0x1010), b1_hi = __byte_perm(scales[1].y, 0, 0x3232);
-          CHORD_PROF_ADD(2, pt1);
-          if (ok) {
-            CHORD_PROF_T(pt3);
-            ptx::tc_fence_after();
-            const uint32_t a_addr = a_lane + slot.s * 32u;
-            ptx::tmem_st_16x128b_x8_scaled(a_addr, lo, a0_lo, a0_hi, a1_lo, a1_hi);
-            ptx::tmem_st_16x128b_x8_scaled(a_addr + (16u << 16), hi, b0_lo, b0_hi, b1_lo, b1_hi);
-            ptx::tmem_wait_st();
-            ptx::tc_fence_before();
-            __syncwarp();
-            CHORD_PROF_ADD(4, pt3);
-            CHORD_PROF_T(pt4);
-            ptx::mbar_arrive_lane0(afull0 + slot.s * 8u, lane);
-            CHORD_PROF_ADD(5, pt4);
-          }
-          last_bar = afree;
-          last_ph = slot.ph;
-          slot.advance(kDecSlots);
+      // One 64-wide step (K half `h` of the current stage).  Returns false if a bounded
+      // wait gave up; the loop below is left at once then, so the common path carries no
+      // "still healthy?" predicates.
+      auto step = [&](auto half, uint32_t st, bool release_weights) -> bool {
+        constexpr int h = decltype(half)::value;
+        CHORD_PROF_T(pt1);
+        // four K16 rows of packed words, two K32 groups of scales
+        uint2 words[4], scales[2];
+        words[0] = ptx::lds64<4096 * h + 0>(st + w_off);
+        words[1] = ptx::lds64<4096 * h + 1024>(st + w_off);
+        words[2] = ptx::lds64<4096 * h + 2048>(st + w_off);
+        words[3] = ptx::lds64<4096 * h + 3072>(st + w_off);
+        scales[0] = ptx::lds64<512 * h + 0>(st + s_off);
+        scales[1] = ptx::lds64<512 * h + 256>(st + s_off);
+        if (release_weights) {
+          // The weight half of the stage goes back to the feeder as soon as its last
+          // words are in registers.
+          __syncwarp();
+          ptx::mbar_arrive_lane0(wempty0 + cur.s * 8u, lane);
         }
+        // The operand slot is free once the MMAs of its previous use have completed.
+        // Waited for here, before the dequantised values exist: with thirty-two of them
+        // live, a wait that has to retry costs a register shuffle.
+        CHORD_PROF_T(pt2);
+        const uint32_t afree = afree0 + slot.s * 8u;
+        if (!ptx::mbar_wait_parked(afree, slot.ph ^ 1u, abort_flag)) return false;
+        CHORD_PROF_ADD(3, pt2);
+        uint32_t lo[16], hi[16];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          unbias_word(words[i].x, lo + 4 * i);
+          unbias_word(words[i].y, hi + 4 * i);
+        }
+        // scales[g].x = {slab A row r, slab A row r+8} of K32 group g; .y = same for slab B.
+        const uint32_t a0_lo = __byte_perm(scales[0].x, 0, 0x1010), a0_hi = __byte_perm(scales[0].x, 0, 0x3232);
+        const uint32_t a1_lo = __byte_perm(scales[1].x, 0, 0x1010), a1_hi = __byte_perm(scales[1].x, 0, 0x3232);
+        const uint32_t b0_lo = __byte_perm(scales[0].y, 0, 0x1010), b0_hi = __byte_perm(scales[0].y, 0, 0x3232);
+        const uint32_t b1_lo = __byte_perm(scales[1].y, 0, 0x1010), b1_hi = __byte_perm(scales[1].y, 0, 0x3232);
+        CHORD_PROF_ADD(2, pt1);
+        CHORD_PROF_T(pt3);
+        ptx::tc_fence_after();
+        const uint32_t a_addr = a_lane + slot.s * 32u;
+        ptx::tmem_st_16x128b_x8_scaled(a_addr, lo, a0_lo, a0_hi, a1_lo, a1_hi);
+        ptx::tmem_st_16x128b_x8_scaled(a_addr + (16u << 16), hi, b0_lo, b0_hi, b1_lo, b1_hi);
+        ptx::tmem_wait_st();
+        ptx::tc_fence_before();
+        __syncwarp();
+        CHORD_PROF_ADD(4, pt3);
+        ptx::mbar_arrive_lane0(afull0 + slot.s * 8u, lane);
+        last_bar = afree;
+        last_ph = slot.ph;
+        slot.advance(kDecSlots);
+        return true;
+      };
+      if (ok) {
+        for (int32_t j = 0; j < n_steps; ++j) {
+          const uint32_t st = ring + cur.s * stage_bytes;
+          const bool two_halves = !(k_tail_half && seg.kb + j == k_steps - 1);
+          CHORD_PROF_T(pt0);
+          ok = ptx::mbar_wait_parked(wfull0 + cur.s * 8u, cur.ph, abort_flag);
+          CHORD_PROF_ADD(1, pt0);
+          if (ok) ok = step(std::integral_constant<int, 0>{}, st, !two_halves);
+          if (ok && two_halves) ok = step(std::integral_constant<int, 1>{}, st, true);
+          if (!ok) break;
+          cur.advance(stages);
+        }
+        // ---- end of the segment: wait for its last MMAs.
+        CHORD_PROF_T(pe0);
+        if (ok) ok = ptx::mbar_wait_parked(last_bar, last_ph, abort_flag);
+        CHORD_PROF_ADD(6, pe0);
         if (!ok) sh.abort_flag = 1;
-        cur.advance(stages);
       }
-      // ---- end of the segment: wait for its last MMAs, then drain the accumulator.
-      CHORD_PROF_T(pe0);
-      if (ok) ok = ptx::mbar_wait_parked(last_bar, last_ph, abort_flag);
-      CHORD_PROF_ADD(6, pe0);
+      // Drain the accumulator.  A warp that has given up skips the work but still meets
+      // its siblings at the named barriers of a stream-K slice, here and for every
+      // segment that follows.
       CHORD_PROF_T(pe1);
       drain(seg, my_out_row, t.n0, col0 + kDecDCol, t.mma_n);
       CHORD_PROF_ADD(7, pe1);
