@@ -517,7 +517,11 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
     const uint32_t w_off = x_bytes + (q >> 1) * 512u + lane * 16u + (q & 1) * 8u;
     const uint32_t s_off = x_bytes + kDecWBytes + (q >> 1) * 128u + (lane >> 2) * 16u + (q & 1) * 8u;
     const uint32_t a_lane = tmem_base + ((q * 32u) << 16) + col0;
-    StageCursor cur, slot;
+    // Ring positions as running byte offsets (no multiplications in the loop): `stage_off`
+    // into the ring, `stage_bar` into the per-stage barrier arrays (8 bytes each),
+    // `slot_bar` into the per-slot barrier arrays; one phase bit each.
+    const uint32_t ring_bytes = stages * stage_bytes;
+    uint32_t stage_off = 0, stage_bar = 0, stage_ph = 0, slot_bar = 0, slot_ph = 0;
     bool ok = true;
     CHORD_PROF_INIT();
     const size_t ws_slot = static_cast<size_t>(kBlockN) * p.mma_n;
@@ -552,14 +556,14 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
           // The weight half of the stage goes back to the feeder as soon as its last
           // words are in registers.
           __syncwarp();
-          ptx::mbar_arrive_lane0(wempty0 + cur.s * 8u, lane);
+          ptx::mbar_arrive_lane0(wempty0 + stage_bar, lane);
         }
         // The operand slot is free once the MMAs of its previous use have completed.
         // Waited for here, before the dequantised values exist: with thirty-two of them
         // live, a wait that has to retry costs a register shuffle.
         CHORD_PROF_T(pt2);
-        const uint32_t afree = afree0 + slot.s * 8u;
-        if (!ptx::mbar_wait_parked(afree, slot.ph ^ 1u, abort_flag)) return false;
+        const uint32_t afree = afree0 + slot_bar;
+        if (!ptx::mbar_wait_parked(afree, slot_ph ^ 1u, abort_flag)) return false;
         CHORD_PROF_ADD(3, pt2);
         uint32_t lo[16], hi[16];
 #pragma unroll
@@ -575,30 +579,40 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
         CHORD_PROF_ADD(2, pt1);
         CHORD_PROF_T(pt3);
         ptx::tc_fence_after();
-        const uint32_t a_addr = a_lane + slot.s * 32u;
+        const uint32_t a_addr = a_lane + slot_bar * 4u;  // 32 columns per slot
         ptx::tmem_st_16x128b_x8_scaled(a_addr, lo, a0_lo, a0_hi, a1_lo, a1_hi);
         ptx::tmem_st_16x128b_x8_scaled(a_addr + (16u << 16), hi, b0_lo, b0_hi, b1_lo, b1_hi);
         ptx::tmem_wait_st();
         ptx::tc_fence_before();
         __syncwarp();
         CHORD_PROF_ADD(4, pt3);
-        ptx::mbar_arrive_lane0(afull0 + slot.s * 8u, lane);
+        ptx::mbar_arrive_lane0(afull0 + slot_bar, lane);
         last_bar = afree;
-        last_ph = slot.ph;
-        slot.advance(kDecSlots);
+        last_ph = slot_ph;
+        slot_bar += 8u;
+        if (slot_bar == 8u * kDecSlots) {
+          slot_bar = 0;
+          slot_ph ^= 1u;
+        }
         return true;
       };
       if (ok) {
         for (int32_t j = 0; j < n_steps; ++j) {
-          const uint32_t st = ring + cur.s * stage_bytes;
+          const uint32_t st = ring + stage_off;
           const bool two_halves = !(k_tail_half && seg.kb + j == k_steps - 1);
           CHORD_PROF_T(pt0);
-          ok = ptx::mbar_wait_parked(wfull0 + cur.s * 8u, cur.ph, abort_flag);
+          ok = ptx::mbar_wait_parked(wfull0 + stage_bar, stage_ph, abort_flag);
           CHORD_PROF_ADD(1, pt0);
           if (ok) ok = step(std::integral_constant<int, 0>{}, st, !two_halves);
           if (ok && two_halves) ok = step(std::integral_constant<int, 1>{}, st, true);
           if (!ok) break;
-          cur.advance(stages);
+          stage_off += stage_bytes;
+          stage_bar += 8u;
+          if (stage_off == ring_bytes) {
+            stage_off = 0;
+            stage_bar = 0;
+            stage_ph ^= 1u;
+          }
         }
         // ---- end of the segment: wait for its last MMAs.
         CHORD_PROF_T(pe0);
