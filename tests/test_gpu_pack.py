@@ -60,3 +60,47 @@ def test_range_check_and_argument_errors(device):
         chord_b200.pack_w4a16(ok, scale[:, :, :1].contiguous())
     with pytest.raises(TypeError):
         chord_b200.pack_w4a16(ok, scale.float())
+
+
+def test_packer_equals_reference_gpu_packer(device):
+    """Bit-exact against the packed words and scales the reference's own pack_w4a16
+    produced on a B200 (tests/golden/reference_gpu.npz)."""
+    from pathlib import Path
+
+    import chord_b200
+
+    z = np.load(Path(__file__).resolve().parent / "golden" / "reference_gpu.npz")
+    scale = torch.from_numpy(z["pack_scale_in"].copy()).view(torch.bfloat16)
+    words = torch.from_numpy(z["pack_words"])
+    got = chord_b200.pack_w4a16(words.to(device), scale.to(device), packed=True)
+    assert np.array_equal(got.packed.cpu().numpy(), z["pack_packed"])
+    assert np.array_equal(got.scale.cpu().contiguous().view(torch.int16).numpy(), z["pack_scale_out"])
+    codes = O.unpack_checkpoint_uint4(words)
+    codes = codes if isinstance(codes, torch.Tensor) else torch.from_numpy(np.asarray(codes))
+    got2 = chord_b200.pack_w4a16(codes.to(torch.int32).to(device), scale.to(device))
+    assert np.array_equal(got2.packed.cpu().numpy(), z["pack_packed"])
+
+
+def test_indexed_agrees_with_reference_gpu_kernel(device):
+    """Same inputs and routing as the reference's own `indexed` launch on a B200: the
+    same rows are written, outputs agree within the BF16 output rounding (both round an
+    FP32 sum once; the summation orders differ)."""
+    from pathlib import Path
+
+    import chord_b200
+
+    z = np.load(Path(__file__).resolve().parent / "golden" / "reference_gpu.npz")
+    e, n, k, m, top_k, block_m = (int(v) for v in z["idx_shape"])
+    bf = lambda a: torch.from_numpy(a.copy()).view(torch.bfloat16)  # noqa: E731
+    weight = chord_b200.pack_w4a16(torch.from_numpy(z["idx_words"]).to(device), bf(z["idx_scale"]).to(device),
+                                   packed=True)
+    out = torch.full((m * top_k, n), float("nan"), dtype=torch.bfloat16, device=device)
+    chord_b200.indexed(bf(z["idx_x"]).to(device), weight, torch.from_numpy(z["idx_sorted_ids"]).to(device),
+                       torch.from_numpy(z["idx_expert_ids"]).to(device),
+                       torch.from_numpy(z["idx_num_tokens_padded"]).to(device), top_k, outputs=out,
+                       block_m=block_m)
+    torch.cuda.synchronize()
+    got, ref = out.float().cpu(), bf(z["idx_out"]).float()
+    assert not torch.isnan(got).any()
+    assert O.cosine_diff(got, ref) <= 1e-5
+    assert O.max_abs_rel(got, ref) <= 1e-2

@@ -129,3 +129,50 @@ def test_empty_routing_is_allowed():
     assert s.numel() == 0 and e.numel() == 0 and int(padded) == 0
     with pytest.raises(ValueError):
         O.align_routing_blocks(topk, 16, 48, 0, allow_empty=False)
+
+
+# ---- pinned by the reference's own GPU kernels (tests/golden/reference_gpu.npz, produced
+# on a B200 by tests/golden/make_reference_gpu_golden.py from the reference's pack_w4a16
+# and indexed)
+
+def _reference_gpu():
+    return np.load(Path(__file__).resolve().parent / "golden" / "reference_gpu.npz")
+
+
+def _bf16(array):
+    return torch.from_numpy(array.copy()).view(torch.bfloat16)
+
+
+def test_packed_layout_equals_reference_gpu_packer():
+    """Packed words and permuted scales, bit for bit, against the output of the
+    reference's repack kernel (include/humming/kernel/repack.cuh) and
+    _pack_weight_scale (operator/packing.py:45-52) run on a B200."""
+    z = _reference_gpu()
+    codes = O.unpack_checkpoint_uint4(torch.from_numpy(z["pack_words"]))
+    codes = codes.numpy() if isinstance(codes, torch.Tensor) else codes
+    assert np.array_equal(np.asarray(O.repack_closed_form(codes)), z["pack_packed"])
+    assert np.array_equal(np.asarray(O.repack_literal(codes)), z["pack_packed"])
+    scale_out = O.permute_scale(_bf16(z["pack_scale_in"]))
+    assert np.array_equal(scale_out.contiguous().view(torch.int16).numpy(), z["pack_scale_out"])
+    # and back: the closed-form inverse recovers the codes from the reference's words
+    assert np.array_equal(np.asarray(O.unpack_closed_form(z["pack_packed"], 256, 320)), codes)
+
+
+def test_oracle_indexed_matches_reference_gpu_kernel():
+    """The CPU restatement against the BF16 output of the reference's own `indexed`
+    kernel (its Blackwell mma.sync schedule) on a B200: same rows written, cosine
+    difference <= 5e-3 (the reference's own limit, tests/test_w4a16_indexed.py:63)."""
+    z = _reference_gpu()
+    e, n, k, m, top_k, block_m = (int(v) for v in z["idx_shape"])
+    codes = O.unpack_checkpoint_uint4(torch.from_numpy(z["idx_words"]))
+    codes = codes if isinstance(codes, torch.Tensor) else torch.from_numpy(np.asarray(codes))
+    topk = torch.from_numpy(z["idx_topk"].astype(np.int64))
+    sorted_ids, expert_ids, padded = O.align_routing_blocks(topk, block_m, e, 0)
+    assert np.array_equal(sorted_ids.numpy(), z["idx_sorted_ids"])
+    assert np.array_equal(expert_ids.numpy(), z["idx_expert_ids"])
+    assert int(padded) == int(z["idx_num_tokens_padded"][0])
+    ref = O.reference_indexed(_bf16(z["idx_x"]), codes, _bf16(z["idx_scale"]), topk, top_k)
+    got = _bf16(z["idx_out"]).float()
+    assert got.shape == ref.shape == (m * top_k, n)
+    assert O.cosine_diff(got, ref) <= 5e-3
+    assert O.max_abs_rel(got, ref) <= 1e-2
