@@ -10,10 +10,13 @@ checked, in ``tests/test_oracle.py``, against golden vectors produced by
 running the reference's own CPU-runnable code (``tests/generators.py`` and
 ``chord_kernels/operator/packing.py::_pack_weight_scale``) - see
 ``tests/golden/make_golden.py``.  The packed-weight layout has no golden vector
-or known-answer test in the reference (its only producer is a CUDA kernel), so
-``repack_literal`` restates that kernel thread by thread and ``repack_closed_form``
-is checked against it; that part of the parity is pinned by restatement of
-``repack.cuh`` only, not by reference output.
+or known-answer test in the reference (its only producer is a CUDA kernel):
+``repack_literal`` restates that kernel thread by thread, ``repack_closed_form`` is
+checked against it, and both are checked bit for bit against the words the
+reference's own ``pack_w4a16`` produced on a B200
+(``tests/golden/reference_gpu.npz``, made by
+``tests/golden/make_reference_gpu_golden.py``); ``reference_indexed`` is checked
+against the BF16 output of the reference's ``indexed`` kernel from the same run.
 """
 
 from __future__ import annotations
