@@ -79,6 +79,21 @@ __host__ __device__ inline uint32_t decode_stage_bytes(int mma_n) {
 // which is the common case at decode sizes whatever block size the routing was
 // aligned to.  A tile without any row is not valid (nothing to compute).  Must be
 // called by all 32 lanes of a warp.
+#ifdef CHORD_TIMELINE
+__device__ __forceinline__ unsigned long long dec_globaltimer() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+#define DEC_STAMP(i, cond) do { if (p.profile && (cond)) p.profile[blockIdx.x * 64 + (i)] = dec_globaltimer(); } while (0)
+#define DEC_STAMP_DECL() bool stamped = false
+#define DEC_STAMPED() stamped = true
+#else
+#define DEC_STAMP(i, cond) do {} while (0)
+#define DEC_STAMP_DECL() do {} while (0)
+#define DEC_STAMPED() do {} while (0)
+#endif
+
 __device__ __forceinline__ TileInfo decode_tile_small(const GemmParams& p, const int32_t* group_prefix,
                                                       int32_t tile) {
   TileInfo t;
@@ -195,9 +210,21 @@ __device__ __noinline__ void decode_drain(uint32_t d_addr, __nv_bfloat16* out_ti
         continue;
       }
       if (seg_type == kSegOwner) {
-        for (int32_t peer = 1; peer <= seg_peer; ++peer) {
-          const float* part = workspace + (worker_id + peer) * ws_slot + static_cast<size_t>(c0) * kBlockN +
-                              q * 32 + lane;
+        // Partials are added in worker order (deterministic); two slices' loads are in
+        // flight at a time, each a round trip to L2.
+        const float* part = workspace + (worker_id + 1) * ws_slot + static_cast<size_t>(c0) * kBlockN +
+                            q * 32 + lane;
+        int32_t peer = 1;
+        for (; peer + 1 <= seg_peer; peer += 2, part += 2 * ws_slot) {
+          float p0[16], p1[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) p0[i] = __ldcg(part + i * kBlockN);
+#pragma unroll
+          for (int i = 0; i < 16; ++i) p1[i] = __ldcg(part + ws_slot + i * kBlockN);
+#pragma unroll
+          for (int i = 0; i < 16; ++i) accv[i] = (accv[i] + p0[i]) + p1[i];
+        }
+        if (peer <= seg_peer) {
 #pragma unroll
           for (int i = 0; i < 16; ++i) accv[i] += __ldcg(part + i * kBlockN);
         }
@@ -236,6 +263,7 @@ __global__ void __launch_bounds__(kDecThreads, 1)
 w4a16_decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_s,
                     const GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
+  DEC_STAMP(0, threadIdx.x == 0);
   // Dynamic shared memory, 1024-aligned: one ring per worker, then DecodeShared.
   const uint32_t raw_addr = ptx::smem_u32(smem_raw);
   uint8_t* smem = smem_raw + ((1024u - (raw_addr & 1023u)) & 1023u);
@@ -251,33 +279,40 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
   const int32_t k_steps = (p.k + kDecStageK - 1) / kDecStageK;  // ring stages per tile
   const bool k_tail_half = (p.k % kDecStageK) != 0;             // last stage: first K half only
 
-  if (threadIdx.x == 0) {
-    ptx::prefetch_tensormap(&tm_w);
-    ptx::prefetch_tensormap(&tm_s);
-    for (int w = 0; w < kDecWorkers; ++w) {
-      for (uint32_t s = 0; s < stages; ++s) {
-        ptx::mbar_init(ptx::smem_u32(&sh.worker[w].wfull[s]), 1);
-        ptx::mbar_init(ptx::smem_u32(&sh.worker[w].wempty[s]), 4);
-        ptx::mbar_init(ptx::smem_u32(&sh.worker[w].xfull[s]), 1);
-        ptx::mbar_init(ptx::smem_u32(&sh.worker[w].xempty[s]), 1);
-      }
-      for (int j = 0; j < kDecSlots; ++j) {
-        ptx::mbar_init(ptx::smem_u32(&sh.worker[w].afull[j]), 4);
-        ptx::mbar_init(ptx::smem_u32(&sh.worker[w].afree[j]), 1);
-      }
+  // Set-up is on the critical path of a small launch (a batch of one token is a
+  // 25 us kernel): one thread per worker initialises that worker's barriers.
+  if (warp >= 4 && warp < 8 && lane == 0) {
+    const uint32_t w = warp - 4;
+    if (w == 0) {
+      ptx::prefetch_tensormap(&tm_w);
+      ptx::prefetch_tensormap(&tm_s);
+      sh.abort_flag = 0;
     }
-    sh.abort_flag = 0;
+    for (uint32_t s = 0; s < stages; ++s) {
+      ptx::mbar_init(ptx::smem_u32(&sh.worker[w].wfull[s]), 1);
+      ptx::mbar_init(ptx::smem_u32(&sh.worker[w].wempty[s]), 4);
+      ptx::mbar_init(ptx::smem_u32(&sh.worker[w].xfull[s]), 1);
+      ptx::mbar_init(ptx::smem_u32(&sh.worker[w].xempty[s]), 1);
+    }
+    for (int j = 0; j < kDecSlots; ++j) {
+      ptx::mbar_init(ptx::smem_u32(&sh.worker[w].afull[j]), 4);
+      ptx::mbar_init(ptx::smem_u32(&sh.worker[w].afree[j]), 1);
+    }
     ptx::fence_barrier_init();
   }
   if (warp == 1) {
     ptx::tmem_alloc(ptx::smem_u32(&sh.tmem_base), kTmemCols);
     ptx::tmem_relinquish();
   }
-  // Activation rows no gather ever fills must not hold NaN patterns.
+  // Activation rows no gather ever fills must not hold NaN patterns: zero the activation
+  // part of every stage (the weight part is always written in full by the TMA).
   {
-    uint4* ring_words = reinterpret_cast<uint4*>(smem);
-    for (uint32_t i = threadIdx.x; i < kDecWorkers * worker_bytes / 16; i += blockDim.x) {
-      ring_words[i] = make_uint4(0, 0, 0, 0);
+    const uint32_t x_vecs = x_bytes / 16;
+    const uint32_t total = kDecWorkers * stages * x_vecs;
+    for (uint32_t i = threadIdx.x; i < total; i += blockDim.x) {
+      const uint32_t stage_index = i / x_vecs;
+      reinterpret_cast<uint4*>(smem + stage_index * stage_bytes)[i - stage_index * x_vecs] =
+          make_uint4(0, 0, 0, 0);
     }
   }
   if (threadIdx.x == 0) {
@@ -303,8 +338,9 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
   __syncthreads();
   ptx::tc_fence_after();
 
+  DEC_STAMP(1, threadIdx.x == 0);
   const uint32_t tmem_base = sh.tmem_base;
-  volatile uint32_t* abort_flag = &sh.abort_flag;
+  const uint32_t abort_addr = ptx::smem_u32(&sh.abort_flag);  // raised by any wait that gives up
   const int32_t tiles = sh.m_blocks * (p.n / kBlockN);
   // warps 0-3 feed, warps 4-7 issue the MMAs, warps 8-23 are the four workers
   const uint32_t wk = warp < 8 ? (warp & 3u) : (warp - 8) >> 2;
@@ -349,13 +385,14 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
     bool x_pending = false;
     const int32_t w_lead = static_cast<int32_t>(stages) - 2;
     int32_t w_ahead = 0;
-    bool w_more = true, ok = true;
+    bool w_more = true;
+    uint32_t bad = 0;
     int32_t w_row = 0, s_row = 0, w_col = 0;
     int32_t x_off[8];
     uint32_t active = 0;  // bit b: some lane has a row to fetch in round b
     const __nv_bfloat16* src = p.x;
     CHORD_PROF_INIT();
-    while (ok) {
+    while (bad == 0) {
       while (w_more && w_ahead <= w_lead) {
         bool first = false;
         if (!wsm.next(p, sh.group_prefix, first)) {
@@ -368,10 +405,8 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
           w_col = wsm.t.n0;
         }
         CHORD_PROF_T(ft0);
-        if (!ptx::mbar_wait_parked(wempty0 + wcur.s * 8u, wcur.ph ^ 1u, abort_flag)) {
-          ok = false;
-          break;
-        }
+        ptx::mbar_wait_sticky(wempty0 + wcur.s * 8u, wcur.ph ^ 1u, abort_addr, bad);
+        if (bad != 0) break;
         CHORD_PROF_ADD(1, ft0);
         CHORD_PROF_T(ft1);
         if (lane == 0) {
@@ -388,7 +423,7 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
         wcur.advance(stages);
         ++w_ahead;
       }
-      if (!ok) break;
+      if (bad != 0) break;
       bool first = false;
       if (!xsm.next(p, sh.group_prefix, first)) break;
       if (first) {
@@ -407,10 +442,8 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
         src = p.x + xsm.kb * kDecStageK + piece * 8;
       }
       CHORD_PROF_T(ft2);
-      if (!ptx::mbar_wait_parked(xempty0 + xcur.s * 8u, xcur.ph ^ 1u, abort_flag)) {
-        ok = false;
-        break;
-      }
+      ptx::mbar_wait_sticky(xempty0 + xcur.s * 8u, xcur.ph ^ 1u, abort_addr, bad);
+      if (bad != 0) break;
       CHORD_PROF_ADD(3, ft2);
       CHORD_PROF_T(ft3);
       const uint32_t xs = ring + xcur.s * stage_bytes;
@@ -446,10 +479,7 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
     __syncwarp();
     if (x_pending && lane == 0) ptx::mbar_arrive(xfull0 + xdone.s * 8u);
     if (wk == 0) CHORD_PROF_FLUSH(2);
-    if (!ok && lane == 0) {
-      sh.abort_flag = 1;
-      if (p.status) atomicOr(p.status, kStatusProducerTimeout);
-    }
+    if (bad != 0 && lane == 0 && p.status) atomicOr(p.status, kStatusProducerTimeout);
     __syncwarp();
   } else if (warp < 8) {
     // ------------------------------------------------- MMA issuer of worker `warp - 4` --
@@ -459,25 +489,22 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
     // feeder with the second one.
     const uint32_t d_tm = tmem_base + col0 + kDecDCol;
     StageCursor cur, slot;
-    bool ok = true;
-    while (ok && iter.next(seg)) {
+    uint32_t bad = 0;
+    while (bad == 0 && iter.next(seg)) {
       const TileInfo t = decode_tile_small(p, sh.group_prefix, seg.tile);
       if (!t.valid) continue;
       const uint32_t idesc = ptx::idesc_bf16_f32(kBlockN, static_cast<uint32_t>(t.mma_n));
       uint32_t acc = 0;
-      for (int32_t kb = seg.kb; ok && kb < seg.ke; ++kb) {
+      for (int32_t kb = seg.kb; bad == 0 && kb < seg.ke; ++kb) {
         // No wait is needed for the accumulator: the first store of a segment follows
         // its warp's share of the previous segment's epilogue.
         const int32_t halves = (k_tail_half && kb == k_steps - 1) ? 1 : 2;
         const uint32_t stage = ring + cur.s * stage_bytes;
         for (int32_t h = 0; h < halves; ++h) {
-          if (!ptx::mbar_wait_parked(afull0 + slot.s * 8u, slot.ph, abort_flag) ||
-              (h == 0 && !ptx::mbar_wait_parked(xfull0 + cur.s * 8u, cur.ph, abort_flag))) {
-            ok = false;
-            break;
-          }
+          ptx::mbar_wait_sticky(afull0 + slot.s * 8u, slot.ph, abort_addr, bad);
+          if (h == 0) ptx::mbar_wait_sticky(xfull0 + cur.s * 8u, cur.ph, abort_addr, bad);
           ptx::tc_fence_after();
-          if (lane == 0) {
+          if (lane == 0 && bad == 0) {
             const uint64_t xdesc = ptx::smem_desc_k_sw128(stage + static_cast<uint32_t>(h) * x_half_bytes);
             const uint32_t a_tm = tmem_base + col0 + slot.s * 32u;
             if (!(DEC_ABLATE & 1)) {
@@ -496,19 +523,17 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
         cur.advance(stages);
       }
     }
-    if (!ok && lane == 0) {
-      sh.abort_flag = 1;
-      if (p.status) atomicOr(p.status, kStatusMmaTimeout);
-    }
+    if (bad != 0 && lane == 0 && p.status) atomicOr(p.status, kStatusMmaTimeout);
     __syncwarp();
   } else {
     // ------------------------------------------------------------- worker warps --
     // Inside a segment the four warps run independently: each waits for the stage,
     // dequantises its 32 weight rows, waits for a free operand slot, stores, and tells
     // the issuer.  They meet (named barriers) only in the epilogue of a stream-K slice.
-    // A warp whose bounded wait gave up clears `ok`, raises the abort flag (so that the
-    // others' waits give up quickly too) and does no more work, but still walks the
-    // remaining segments and meets its siblings at those barriers.
+    // A warp whose bounded wait gave up keeps `bad` set (and the CTA's abort flag raised,
+    // so that the others' waits give up quickly too), leaves the stage loop at the end
+    // of that stage and does no more work, but still walks the remaining segments and
+    // meets its siblings at those barriers.
     const uint32_t q = warp & 3;                          // TMEM lane quarter == 32 weight rows
     const uint32_t wt = threadIdx.x - (8 + 4 * wk) * 32;  // 0..127 inside the worker
     const uint32_t bar_id = 1 + wk;
@@ -522,26 +547,29 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
     // `slot_bar` into the per-slot barrier arrays; one phase bit each.
     const uint32_t ring_bytes = stages * stage_bytes;
     uint32_t stage_off = 0, stage_bar = 0, stage_ph = 0, slot_bar = 0, slot_ph = 0;
-    bool ok = true;
+    uint32_t bad = 0;  // sticky: set by the first bounded wait that gives up
     CHORD_PROF_INIT();
+    DEC_STAMP_DECL();
     const size_t ws_slot = static_cast<size_t>(kBlockN) * p.mma_n;
 
     auto drain = [&](const Segment& sg, int32_t rows, int32_t n0, uint32_t dcol, int32_t mma_n) {
       decode_drain(tmem_base + ((q * 32u) << 16) + dcol, p.out + n0 + q * 32, p.n, rows, mma_n, sg.type,
                    sg.peer, p.workspace, ws_slot, worker_id, p.locks, p.status, &ws.stage[q][0][0], bar_id,
-                   wt, ok);
+                   wt, bad == 0);
     };
     while (iter.next(seg)) {
       const TileInfo t = decode_tile_small(p, sh.group_prefix, seg.tile);
       if (!t.valid) continue;
-      const int32_t n_steps = seg.ke - seg.kb;
+      // The segment's last stage holds one K half only when K is an odd multiple of 64.
+      const bool tail = k_tail_half && seg.ke == k_steps;
+      const int32_t n_full = seg.ke - seg.kb - (tail ? 1 : 0);
       // Output row of token slot `lane`: loaded now, used in the epilogue.
       const int32_t my_out_row = out_row_of(p, t, static_cast<int32_t>(lane));
-      uint32_t last_bar = 0, last_ph = 0;
-      // One 64-wide step (K half `h` of the current stage).  Returns false if a bounded
-      // wait gave up; the loop below is left at once then, so the common path carries no
-      // "still healthy?" predicates.
-      auto step = [&](auto half, uint32_t st, bool release_weights) -> bool {
+      uint32_t last_bar = afree0, last_ph = slot_ph ^ 1u;
+      // One 64-wide step (K half `h` of the stage at `st`), straight-line: the waits
+      // record a failure in `bad` and the code runs on (on stale data, within this
+      // worker's own shared and tensor memory); `bad` is tested once per stage.
+      auto step = [&](auto half, uint32_t st, bool release_weights) {
         constexpr int h = decltype(half)::value;
         CHORD_PROF_T(pt1);
         // four K16 rows of packed words, two K32 groups of scales
@@ -559,11 +587,10 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
           ptx::mbar_arrive_lane0(wempty0 + stage_bar, lane);
         }
         // The operand slot is free once the MMAs of its previous use have completed.
-        // Waited for here, before the dequantised values exist: with thirty-two of them
-        // live, a wait that has to retry costs a register shuffle.
+        // Waited for here, before the dequantised values exist.
         CHORD_PROF_T(pt2);
         const uint32_t afree = afree0 + slot_bar;
-        if (!ptx::mbar_wait_parked(afree, slot_ph ^ 1u, abort_flag)) return false;
+        ptx::mbar_wait_sticky(afree, slot_ph ^ 1u, abort_addr, bad);
         CHORD_PROF_ADD(3, pt2);
         uint32_t lo[16], hi[16];
 #pragma unroll
@@ -594,48 +621,55 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
           slot_bar = 0;
           slot_ph ^= 1u;
         }
-        return true;
       };
-      if (ok) {
-        for (int32_t j = 0; j < n_steps; ++j) {
+      auto next_stage = [&]() {
+        stage_off += stage_bytes;
+        stage_bar += 8u;
+        if (stage_off == ring_bytes) {
+          stage_off = 0;
+          stage_bar = 0;
+          stage_ph ^= 1u;
+        }
+      };
+      if (bad == 0) {
+        for (int32_t j = 0; j < n_full; ++j) {
           const uint32_t st = ring + stage_off;
-          const bool two_halves = !(k_tail_half && seg.kb + j == k_steps - 1);
           CHORD_PROF_T(pt0);
-          ok = ptx::mbar_wait_parked(wfull0 + stage_bar, stage_ph, abort_flag);
+          ptx::mbar_wait_sticky(wfull0 + stage_bar, stage_ph, abort_addr, bad);
           CHORD_PROF_ADD(1, pt0);
-          if (ok) ok = step(std::integral_constant<int, 0>{}, st, !two_halves);
-          if (ok && two_halves) ok = step(std::integral_constant<int, 1>{}, st, true);
-          if (!ok) break;
-          stage_off += stage_bytes;
-          stage_bar += 8u;
-          if (stage_off == ring_bytes) {
-            stage_off = 0;
-            stage_bar = 0;
-            stage_ph ^= 1u;
-          }
+          DEC_STAMP(2, wt == 0 && wk == 0 && !stamped);
+          step(std::integral_constant<int, 0>{}, st, false);
+          step(std::integral_constant<int, 1>{}, st, true);
+          next_stage();
+          if (bad != 0) break;
+        }
+        if (tail && bad == 0) {
+          ptx::mbar_wait_sticky(wfull0 + stage_bar, stage_ph, abort_addr, bad);
+          step(std::integral_constant<int, 0>{}, ring + stage_off, true);
+          next_stage();
         }
         // ---- end of the segment: wait for its last MMAs.
         CHORD_PROF_T(pe0);
-        if (ok) ok = ptx::mbar_wait_parked(last_bar, last_ph, abort_flag);
+        if (bad == 0) ptx::mbar_wait_sticky(last_bar, last_ph, abort_addr, bad);
         CHORD_PROF_ADD(6, pe0);
-        if (!ok) sh.abort_flag = 1;
       }
+      DEC_STAMP(3, wt == 0 && wk == 0 && !stamped);
       // Drain the accumulator.  A warp that has given up skips the work but still meets
       // its siblings at the named barriers of a stream-K slice, here and for every
       // segment that follows.
       CHORD_PROF_T(pe1);
       drain(seg, my_out_row, t.n0, col0 + kDecDCol, t.mma_n);
       CHORD_PROF_ADD(7, pe1);
+      DEC_STAMP(4, wt == 0 && wk == 0 && !stamped);
+      DEC_STAMPED();
     }
     if (wk == 0 && q < 2) CHORD_PROF_FLUSH(q);
-    if (!ok && lane == 0) {
-      sh.abort_flag = 1;
-      if (p.status) atomicOr(p.status, kStatusDequantTimeout);
-    }
+    if (bad != 0 && lane == 0 && p.status) atomicOr(p.status, kStatusDequantTimeout);
   }
 
   ptx::tc_fence_before();
   __syncthreads();
+  DEC_STAMP(5, threadIdx.x == 0);
   if (warp == 1) {
     ptx::tc_fence_after();
     ptx::tmem_dealloc(tmem_base, kTmemCols);
