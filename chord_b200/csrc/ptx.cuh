@@ -173,7 +173,9 @@ __device__ __forceinline__ bool mbar_wait_parked(uint32_t bar, uint32_t parity,
 // The same bounded wait with a sticky failure word instead of a result to branch on:
 // `bad` stays 0 while every wait so far was satisfied and becomes 1 when one gives up
 // (2^19 failed tries, or the CTA's abort flag seen non-zero, or `bad` already set on
-// entry and the first try failing).  A wait that gives up also raises the abort flag.
+// entry and the first two tries failing).  A failed try has suspended the warp until the
+// phase completed or some microseconds passed, so the second try usually succeeds: the
+// abort flag is looked at only after it.  A wait that gives up also raises the abort flag.
 // The loop lives in one asm statement, so that the satisfied case is the try and one
 // branch, with no compiler-visible control flow around it; the caller tests `bad` where
 // it is cheap (once per stage), not after every wait.
@@ -187,12 +189,12 @@ __device__ __forceinline__ void mbar_wait_sticky(uint32_t bar, uint32_t parity, 
       "@p bra WAIT_DONE;\n\t"
       "mov.u32 n, 0;\n\t"
       "WAIT_RETRY:\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "@p bra WAIT_DONE;\n\t"
       "ld.volatile.shared::cta.u32 f, [%3];\n\t"
       "or.b32 f, f, %0;\n\t"
       "setp.ne.u32 q, f, 0;\n\t"
       "@q bra WAIT_FAIL;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "@p bra WAIT_DONE;\n\t"
       "add.u32 n, n, 1;\n\t"
       "setp.lt.u32 q, n, 524288;\n\t"
       "@q bra WAIT_RETRY;\n\t"
