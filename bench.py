@@ -559,9 +559,9 @@ def main():
                                     else "w4a16_gemm_kernel") + " (gate_up + down launches)",
                          "algorithmic_bytes_per_step": gemm_bytes,
                          # dram__bytes_read+write of one ncu capture of both launches at batch
-                         # 256 (1208.4 MB for 48 reached experts), scaled by the experts this
+                         # 256 (1208.0 MB for 48 reached experts), scaled by the experts this
                          # step reaches
-                         "traffic": 1208.4e6 * workload.active / 48.0,
+                         "traffic": 1208.0e6 * workload.active / 48.0,
                          "traffic_source": "profiles/w4a16_decode_kernel_k25_ep8_decode.md"},
             "cpu_baseline": cpu,
             "e2e": {"value": e2e_ms * 1e3, "unit": "us", "h2d_bytes_per_step": workload.h2d_bytes,
