@@ -104,7 +104,8 @@ __device__ __forceinline__ TileInfo decode_tile_small(const GemmParams& p, const
   t.limit = 0;
   t.mma_n = p.mma_n;
   if (p.mode == kModeIndexed) {
-    t.expert = __ldg(p.expert_ids + mb);
+    // (through a shuffle: a loaded value is not known to be the same in all lanes)
+    t.expert = __shfl_sync(0xffffffffu, __ldg(p.expert_ids + mb), 0);
     t.ntok = p.tile_tokens;
     t.base = mb * p.tile_tokens;
     const int32_t lane = static_cast<int32_t>(threadIdx.x & 31u);
@@ -118,9 +119,10 @@ __device__ __forceinline__ TileInfo decode_tile_small(const GemmParams& p, const
       const int32_t mid = (lo + hi) >> 1;
       if (group_prefix[mid] <= mb) lo = mid; else hi = mid;
     }
+    lo = __shfl_sync(0xffffffffu, lo, 0);
     t.expert = lo;
-    t.m0 = (mb - group_prefix[lo]) * p.tile_tokens;
-    int32_t mm = __ldg(p.masked_m + lo);
+    t.m0 = __shfl_sync(0xffffffffu, (mb - group_prefix[lo]) * p.tile_tokens, 0);
+    int32_t mm = __shfl_sync(0xffffffffu, __ldg(p.masked_m + lo), 0);
     mm = mm < 0 ? 0 : (mm > p.max_m ? p.max_m : mm);
     t.limit = mm;
     const int32_t left = mm - t.m0;
@@ -274,7 +276,10 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
   const uint32_t worker_bytes = stages * stage_bytes;
   DecodeShared& sh = *reinterpret_cast<DecodeShared*>(smem + kDecWorkers * worker_bytes);
 
-  const uint32_t warp = threadIdx.x >> 5;
+  // Read back through a shuffle so that the compiler knows the warp index (and every
+  // ring position, barrier and tensor-memory address derived from it) to be the same in
+  // all lanes and keeps them in uniform registers.
+  const uint32_t warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0);
   const uint32_t lane = threadIdx.x & 31;
   const int32_t k_steps = (p.k + kDecStageK - 1) / kDecStageK;  // ring stages per tile
   const bool k_tail_half = (p.k % kDecStageK) != 0;             // last stage: first K half only
@@ -339,7 +344,7 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
   ptx::tc_fence_after();
 
   DEC_STAMP(1, threadIdx.x == 0);
-  const uint32_t tmem_base = sh.tmem_base;
+  const uint32_t tmem_base = __shfl_sync(0xffffffffu, sh.tmem_base, 0);  // uniform, see `warp`
   const uint32_t abort_addr = ptx::smem_u32(&sh.abort_flag);  // raised by any wait that gives up
   const int32_t tiles = sh.m_blocks * (p.n / kBlockN);
   // warps 0-3 feed, warps 4-7 issue the MMAs, warps 8-23 are the four workers

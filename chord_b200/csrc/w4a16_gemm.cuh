@@ -459,7 +459,10 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
   uint8_t* smem_s = smem_w + w_stages * kWStageBytes;
   GemmShared& sh = *reinterpret_cast<GemmShared*>(smem_s + w_stages * kSStageBytes);
 
-  const uint32_t warp = threadIdx.x >> 5;
+  // Read back through a shuffle so that the compiler knows the warp index (and what is
+  // derived from it: roles, ring positions, barrier and tensor-memory addresses) to be
+  // the same in all lanes and keeps them in uniform registers.
+  const uint32_t warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0);
   const uint32_t lane = threadIdx.x & 31;
   constexpr uint32_t kFirstIssuerWarp = 4;
   constexpr uint32_t kFirstDequantWarp = 8;
@@ -598,7 +601,7 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
   __syncthreads();
   ptx::tc_fence_after();
 
-  const uint32_t tmem_base = sh.tmem_base;
+  const uint32_t tmem_base = __shfl_sync(0xffffffffu, sh.tmem_base, 0);  // uniform, see `warp`
   volatile uint32_t* abort_flag = &sh.abort_flag;
   const int32_t tiles = sh.m_blocks * (p.n / kBlockN);
   SegmentIterator iter;
