@@ -346,7 +346,7 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
   DEC_STAMP(1, threadIdx.x == 0);
   const uint32_t tmem_base = __shfl_sync(0xffffffffu, sh.tmem_base, 0);  // uniform, see `warp`
   const uint32_t abort_addr = ptx::smem_u32(&sh.abort_flag);  // raised by any wait that gives up
-  const int32_t tiles = sh.m_blocks * (p.n / kBlockN);
+  const int32_t tiles = __shfl_sync(0xffffffffu, sh.m_blocks, 0) * (p.n / kBlockN);
   // warps 0-3 feed, warps 4-7 issue the MMAs, warps 8-23 are the four workers
   const uint32_t wk = warp < 8 ? (warp & 3u) : (warp - 8) >> 2;
   // Worker ids interleave the CTAs (worker w of CTA c is c + w * grid), so that a launch

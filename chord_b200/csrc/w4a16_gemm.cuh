@@ -603,7 +603,7 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
 
   const uint32_t tmem_base = __shfl_sync(0xffffffffu, sh.tmem_base, 0);  // uniform, see `warp`
   volatile uint32_t* abort_flag = &sh.abort_flag;
-  const int32_t tiles = sh.m_blocks * (p.n / kBlockN);
+  const int32_t tiles = __shfl_sync(0xffffffffu, sh.m_blocks, 0) * (p.n / kBlockN);
   SegmentIterator iter;
   iter.init(tiles, k_iters, static_cast<int32_t>(gridDim.x), static_cast<int32_t>(blockIdx.x));
   Segment seg;
