@@ -156,22 +156,9 @@ __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity,
   return __all_sync(__activemask(), ok);
 }
 
-// Bounded wait built on the single-instruction try_wait alone: a failed try has already
+// Bounded wait built on the single-instruction try_wait alone (a failed try has already
 // parked the warp for microseconds, so the loop needs neither a sleep nor a clock, only a
-// try count (2^19 tries of ~4 us: about two seconds) and the abort flag.  Whole-warp
-// call; the try is one warp-wide instruction, so every lane sees the same outcome.
-__device__ __forceinline__ bool mbar_wait_parked(uint32_t bar, uint32_t parity,
-                                                 volatile uint32_t* abort_flag) {
-#pragma unroll 1
-  for (uint32_t tries = 0; tries < (1u << 19); ++tries) {
-    if (mbar_try_wait<false>(bar, parity)) return true;
-    if (*abort_flag != 0) break;
-  }
-  return false;
-}
-
-// The same bounded wait with a sticky failure word instead of a result to branch on:
-// `bad` stays 0 while every wait so far was satisfied and becomes 1 when one gives up
+// try count), with a sticky failure word instead of a result to branch on: `bad` stays 0 while every wait so far was satisfied and becomes 1 when one gives up
 // (2^19 failed tries, or the CTA's abort flag seen non-zero, or `bad` already set on
 // entry and the first two tries failing).  A failed try has suspended the warp until the
 // phase completed or some microseconds passed, so the second try usually succeeds: the
