@@ -26,6 +26,8 @@ _EXPORTS = {
     "PreparedWeight": "chord_b200.packing",
     "silu_mul": "chord_b200.fused_ops",
     "moe_align_block_size": "chord_b200.fused_ops",
+    "check_status": "chord_b200.indexed_gemm",
+    "set_option": "chord_b200._lib",
 }
 
 

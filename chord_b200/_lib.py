@@ -39,9 +39,9 @@ SIGNATURES = {
                                                  _ptr, _i64, _ptr, _i64, _i64, _i64, _i64, _i64, _i64,
                                                  _ptr]),
     "chord_b200_contiguous": (_int, [_ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _i64, _ptr, _i64, _ptr,
-                                     _i64, _i64, _i64, _i64, _ptr]),
+                                     _i64, _i64, _i64, _i64, _int, _ptr]),
     "chord_b200_masked": (_int, [_ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _i64, _ptr, _i64, _ptr,
-                                 _i64, _i64, _i64, _i64, _i64, _ptr]),
+                                 _i64, _i64, _i64, _i64, _i64, _int, _ptr]),
     "chord_b200_silu_mul": (_int, [_ptr, _ptr, _i64, _i64, _ptr]),
     "chord_b200_silu_mul_routed": (_int, [_ptr, _ptr, _ptr, _i64, _ptr, _i64, _i64, _ptr]),
     "chord_b200_moe_align_block_size": (_int, [_ptr, _i64, _i64, _i64, _i64, _ptr, _i64, _ptr,
@@ -86,6 +86,7 @@ def _apply_env_options(lib: ctypes.CDLL) -> None:
         ("CHORD_B200_KSPLIT", "ksplit"),
         ("CHORD_B200_PREGATHER", "pregather"),
         ("CHORD_B200_DECODE_KERNEL", "decode_kernel"),
+        ("CHORD_B200_PDL", "pdl"),
     ):
         value = os.environ.get(env)
         if value is None:

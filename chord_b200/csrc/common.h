@@ -7,6 +7,7 @@
 
 #include <cstdarg>
 #include <cstdio>
+#include <shared_mutex>
 #include <string>
 
 namespace chord {
@@ -71,9 +72,35 @@ struct Options {
   int decode_kernel = 1;   // 1 = token tiles of <= 32 rows (indexed, masked) use the warpgroup-per-worker kernel; 0 = never
   int max_stages = 0;      // 0 = as many as fit
   int grid_limit = 0;      // 0 = one CTA per SM
-  int ablate = 0;          // CHORD_PROFILE builds: bit mask of work to skip in timing studies
-  long long profile_buffer = 0;  // device pointer for per-CTA cycle counters (CHORD_PROFILE builds)
+  int pdl = 0;             // 1 = `indexed` launches carry the programmatic stream-serialization attribute
+  int lock_spins = 1 << 22;  // polls (64 ns apart) of a stream-K owner on its lock word before it gives up
 };
 Options& options();
+
+// Kernel launch with, optionally, the programmatic stream-serialization attribute
+// (programmatic dependent launch): the kernel may then become resident while its
+// predecessor in the stream drains, and synchronises with it through
+// griddepcontrol.wait.  The reference sets the same attribute for `enable_pdl`
+// (chord_kernels/operator/csrc/launcher/launcher.cpp:440-451).
+template <typename... Params, typename... Args>
+inline cudaError_t launch_kernel(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem,
+                                 cudaStream_t stream, bool pdl, Args&&... args) {
+  cudaLaunchConfig_t config = {};
+  config.gridDim = grid;
+  config.blockDim = block;
+  config.dynamicSmemBytes = smem;
+  config.stream = stream;
+  cudaLaunchAttribute attribute[1];
+  attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute[0].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attribute;
+  config.numAttrs = pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&config, kernel, static_cast<Params>(args)...);
+}
+// chord_b200_set_option() writes the options under the exclusive lock; every entry
+// point that reads them holds the shared lock for the length of its host-side work, so
+// a launch sees one consistent set.
+std::shared_mutex& options_mutex();
+using OptionsReadLock = std::shared_lock<std::shared_mutex>;
 
 }  // namespace chord

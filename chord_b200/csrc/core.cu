@@ -17,6 +17,11 @@ Options& options() {
   return opts;
 }
 
+std::shared_mutex& options_mutex() {
+  static std::shared_mutex mutex;
+  return mutex;
+}
+
 int current_device_info(DeviceInfo* info) {
   constexpr int kMaxDevices = 64;
   static DeviceInfo cache[kMaxDevices];
@@ -63,6 +68,7 @@ int chord_b200_set_option(const char* name, int64_t value) {
   using chord::fail;
   using chord::kInvalidArgument;
   if (name == nullptr) return fail(kInvalidArgument, "option name is null");
+  std::unique_lock<std::shared_mutex> guard(chord::options_mutex());
   chord::Options& o = chord::options();
   if (!std::strcmp(name, "x_load")) {
     if (value != 0 && value != 1) return fail(kInvalidArgument, "x_load must be 0 or 1");
@@ -96,10 +102,12 @@ int chord_b200_set_option(const char* name, int64_t value) {
   } else if (!std::strcmp(name, "grid_limit")) {
     if (value < 0) return fail(kInvalidArgument, "grid_limit must be >= 0");
     o.grid_limit = static_cast<int>(value);
-  } else if (!std::strcmp(name, "ablate")) {
-    o.ablate = static_cast<int>(value);
-  } else if (!std::strcmp(name, "profile_buffer")) {
-    o.profile_buffer = static_cast<long long>(value);
+  } else if (!std::strcmp(name, "pdl")) {
+    if (value != 0 && value != 1) return fail(kInvalidArgument, "pdl must be 0 or 1");
+    o.pdl = static_cast<int>(value);
+  } else if (!std::strcmp(name, "lock_spins")) {
+    if (value < 1 || value > (1 << 24)) return fail(kInvalidArgument, "lock_spins must be in [1, 2^24]");
+    o.lock_spins = static_cast<int>(value);
   } else {
     return fail(kInvalidArgument, "unknown option '%s'", name);
   }

@@ -5,6 +5,7 @@
 
 #include "../../include/chord_b200.h"
 #include "common.h"
+#include "ptx.cuh"
 
 namespace chord {
 namespace {
@@ -32,6 +33,7 @@ __device__ __forceinline__ void silu_mul_vec8(const __nv_bfloat16* in_row, __nv_
 __global__ void __launch_bounds__(256)
 silu_mul_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfloat16* __restrict__ out,
                 int64_t rows, int64_t inter) {
+  ptx::grid_dependency_wait();
   const int64_t vec_per_row = inter / 8;
   const int64_t total = rows * vec_per_row;
   for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
@@ -46,6 +48,7 @@ silu_mul_routed_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfloat16* __re
                        const int32_t* __restrict__ sorted_ids, int64_t sorted_len,
                        const int32_t* __restrict__ num_tokens_padded, int64_t row_limit,
                        int64_t inter) {
+  ptx::grid_dependency_wait();
   int64_t count = __ldg(num_tokens_padded);
   count = count < 0 ? 0 : (count > sorted_len ? sorted_len : count);
   for (int64_t slot = blockIdx.x; slot < count; slot += gridDim.x) {
@@ -149,13 +152,16 @@ int chord_b200_silu_mul(const void* in, void* out, int64_t rows, int64_t inter, 
   CHORD_REQUIRE(in != nullptr && out != nullptr, "null tensor pointer");
   CHORD_REQUIRE(rows >= 0 && inter > 0 && inter % 8 == 0,
                 "need rows >= 0 and a positive intermediate size divisible by 8");
+  CHORD_REQUIRE(((reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(out)) & 15u) == 0,
+                "in and out must be 16-byte aligned");
   if (rows == 0) return chord::kOk;
   const int64_t total = rows * (inter / 8);
   int64_t blocks = (total + 255) / 256;
   if (blocks > 148 * 16) blocks = 148 * 16;
-  chord::silu_mul_kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const __nv_bfloat16*>(in), static_cast<__nv_bfloat16*>(out), rows, inter);
-  CHORD_CUDA(cudaGetLastError());
+  CHORD_CUDA(chord::launch_kernel(chord::silu_mul_kernel, dim3(static_cast<unsigned>(blocks)), dim3(256), 0,
+                                  static_cast<cudaStream_t>(stream), chord::options().pdl != 0,
+                                  static_cast<const __nv_bfloat16*>(in), static_cast<__nv_bfloat16*>(out),
+                                  rows, inter));
   return chord::kOk;
 }
 
@@ -166,13 +172,15 @@ int chord_b200_silu_mul_routed(const void* in, void* out, const int32_t* sorted_
                     num_tokens_padded != nullptr,
                 "null tensor pointer");
   CHORD_REQUIRE(inter > 0 && inter % 8 == 0, "intermediate size must be a positive multiple of 8");
+  CHORD_REQUIRE(((reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(out)) & 15u) == 0,
+                "in and out must be 16-byte aligned");
   if (sorted_len <= 0) return chord::kOk;
   const int64_t blocks = sorted_len < 148 * 8 ? sorted_len : 148 * 8;
-  chord::silu_mul_routed_kernel<<<static_cast<unsigned>(blocks), 256, 0,
-                                  static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const __nv_bfloat16*>(in), static_cast<__nv_bfloat16*>(out), sorted_ids,
-      sorted_len, num_tokens_padded, row_limit, inter);
-  CHORD_CUDA(cudaGetLastError());
+  CHORD_CUDA(chord::launch_kernel(chord::silu_mul_routed_kernel, dim3(static_cast<unsigned>(blocks)),
+                                  dim3(256), 0, static_cast<cudaStream_t>(stream),
+                                  chord::options().pdl != 0, static_cast<const __nv_bfloat16*>(in),
+                                  static_cast<__nv_bfloat16*>(out), sorted_ids, sorted_len,
+                                  num_tokens_padded, row_limit, inter));
   return chord::kOk;
 }
 

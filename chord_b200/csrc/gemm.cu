@@ -148,8 +148,8 @@ int launch_with_groups(const CUtensorMap& tm_w, const CUtensorMap& tm_s, const C
                 cudaGetErrorString(attr_result[device & 63]));
   }
   const int threads = 32 * (12 + 4 * kGroups);
-  w4a16_gemm_kernel<kGroups><<<grid, threads, smem, stream>>>(tm_w, tm_s, tm_x, p);
-  CHORD_CUDA(cudaGetLastError());
+  CHORD_CUDA(launch_kernel(w4a16_gemm_kernel<kGroups>, dim3(grid), dim3(threads), smem, stream,
+                           p.pdl != 0, tm_w, tm_s, tm_x, p));
   return kOk;
 }
 
@@ -240,8 +240,8 @@ int launch_decode(GemmParams p, const DeviceInfo& dev, const int32_t* packed, co
     return fail(kCudaError, "cudaFuncSetAttribute failed: %s",
                 cudaGetErrorString(attr_result[device & 63]));
   }
-  w4a16_decode_kernel<<<grid, kDecThreads, smem, stream>>>(tm_w, tm_s, p);
-  CHORD_CUDA(cudaGetLastError());
+  CHORD_CUDA(launch_kernel(w4a16_decode_kernel, dim3(grid), dim3(kDecThreads), smem, stream,
+                           p.pdl != 0, tm_w, tm_s, p));
   return kOk;
 }
 
@@ -249,9 +249,7 @@ int launch_decode(GemmParams p, const DeviceInfo& dev, const int32_t* packed, co
 // pipeline depth, scratch checks, launch.
 int launch_gemm(GemmParams p, const void* x, const int32_t* packed, const void* scale,
                 int64_t num_locks, int64_t workspace_bytes, void* stream) {
-  DeviceInfo dev;
-  if (int rc = current_device_info(&dev)) return rc;
-  if (int rc = require_blackwell(dev)) return rc;
+  OptionsReadLock options_guard(options_mutex());
   CHORD_REQUIRE(p.n > 0 && p.n % kBlockN == 0, "N=%d must be a positive multiple of 128", p.n);
   CHORD_REQUIRE(p.k > 0 && p.k % 64 == 0, "K=%d must be a positive multiple of 64", p.k);
   CHORD_REQUIRE(p.num_experts > 0, "num_experts must be positive");
@@ -265,15 +263,25 @@ int launch_gemm(GemmParams p, const void* x, const int32_t* packed, const void* 
                     static_cast<int64_t>(p.x_rows) < (1ll << 31) - 1,
                 "tensor too large for 32-bit TMA coordinates");
 
-  CHORD_REQUIRE(static_cast<int64_t>(p.x_rows) * p.k < (1ll << 31),
-                "activation tensor too large for 32-bit element offsets");
+  // Both kernels read activation rows in 16-byte pieces (cp.async, TMA) and write the
+  // FP32 partial sums as words.
+  CHORD_REQUIRE((reinterpret_cast<uintptr_t>(x) & 15u) == 0,
+                "the activation tensor must be 16-byte aligned");
+  CHORD_REQUIRE((reinterpret_cast<uintptr_t>(p.workspace) & 15u) == 0,
+                "the workspace must be 16-byte aligned");
+  // The row gathers (decode kernel, in-kernel gather of `indexed`) address activations
+  // by 32-bit element offsets; tiled TMA loads use row coordinates and have no such limit.
+  const bool offsets_fit = static_cast<int64_t>(p.x_rows) * p.k < (1ll << 31);
+  DeviceInfo dev;
+  if (int rc = current_device_info(&dev)) return rc;
+  if (int rc = require_blackwell(dev)) return rc;
   const int grid = grid_size(dev);
   p.mma_n = round_up16(p.tile_tokens);
-  p.profile = reinterpret_cast<unsigned long long*>(options().profile_buffer);
-  p.ablate = options().ablate;
+  p.lock_spins = options().lock_spins;
+  if (options().pdl != 0) p.pdl = 1;
   // The decode kernel runs when the caller's locks and scratch are large enough for
   // one per warpgroup; with the smaller buffers of the general kernel, that one runs.
-  if (decode_kernel_applies(p) && p.locks != nullptr && p.workspace != nullptr &&
+  if (decode_kernel_applies(p) && offsets_fit && p.locks != nullptr && p.workspace != nullptr &&
       num_locks >= decode_workers(grid) && workspace_bytes >= decode_workspace_bytes(grid, p.mma_n)) {
     p.num_locks = static_cast<int32_t>(num_locks);
     return launch_decode(p, dev, packed, scale, grid, static_cast<cudaStream_t>(stream));
@@ -286,13 +294,13 @@ int launch_gemm(GemmParams p, const void* x, const int32_t* packed, const void* 
   if (p.mode == kModeIndexed && pregather_applies(p.mma_n) && p.sorted_len > 0) {
     const int64_t offset = stream_k_bytes(grid, p.mma_n);
     const int64_t bytes = static_cast<int64_t>(p.sorted_len) * p.k * 2;
-    if (workspace_bytes >= offset + bytes && static_cast<int64_t>(p.sorted_len) * p.k < (1ll << 31) &&
-        (reinterpret_cast<uintptr_t>(p.workspace) & 15u) == 0 &&
-        (reinterpret_cast<uintptr_t>(x) & 15u) == 0) {
+    if (workspace_bytes >= offset + bytes) {
       gathered = reinterpret_cast<__nv_bfloat16*>(reinterpret_cast<uint8_t*>(p.workspace) + offset);
       p.x_load = kXLoadTiled;
     }
   }
+  CHORD_REQUIRE(p.x_load == kXLoadTiled || offsets_fit,
+                "activation tensor too large for the 32-bit element offsets of the row gather");
   p.x_stages = pick_x_stages(p.mma_n);
   p.w_stages = pick_w_stages(dev, p.mma_n, p.x_stages);
   CHORD_REQUIRE(p.w_stages >= 2, "token tile %d leaves room for fewer than two pipeline stages",
@@ -432,6 +440,7 @@ int chord_b200_masked_tile_m(int64_t expected_m) {
 }
 
 int64_t chord_b200_gemm_workspace_bytes(int64_t tile_tokens) {
+  chord::OptionsReadLock options_guard(chord::options_mutex());
   chord::DeviceInfo dev;
   if (chord::current_device_info(&dev)) return -1;
   if (tile_tokens <= 0 || tile_tokens > chord::kMaxTileTokens) {
@@ -446,6 +455,7 @@ int64_t chord_b200_gemm_workspace_bytes(int64_t tile_tokens) {
 }
 
 int64_t chord_b200_indexed_workspace_bytes(int64_t block_m, int64_t sorted_len, int64_t k) {
+  chord::OptionsReadLock options_guard(chord::options_mutex());
   chord::DeviceInfo dev;
   if (chord::current_device_info(&dev)) return -1;
   if (block_m <= 0 || block_m > chord::kMaxTileTokens || sorted_len < 0 || k <= 0) {
@@ -461,6 +471,7 @@ int64_t chord_b200_indexed_workspace_bytes(int64_t block_m, int64_t sorted_len, 
 }
 
 int chord_b200_gemm_lock_words(void) {
+  chord::OptionsReadLock options_guard(chord::options_mutex());
   chord::DeviceInfo dev;
   if (chord::current_device_info(&dev)) return -1;
   return chord::decode_workers(chord::grid_size(dev));
@@ -542,7 +553,11 @@ int chord_b200_indexed_static_scratch(const void* x, const int32_t* packed, cons
                 chord::kStaticScratchTokens, static_cast<long long>(block_m));
   chord::DeviceInfo dev;
   if (int rc = chord::current_device_info(&dev)) return rc;
-  const int grid = chord::grid_size(dev);
+  int grid = 0;
+  {
+    chord::OptionsReadLock options_guard(chord::options_mutex());
+    grid = chord::grid_size(dev);
+  }
   CHORD_REQUIRE(grid <= chord::kStaticScratchCtas,
                 "the built-in scratch serves at most %d CTAs, this GPU would launch %d; "
                 "use chord_b200_indexed with a caller-provided workspace",
@@ -561,7 +576,7 @@ int chord_b200_indexed_static_scratch(const void* x, const int32_t* packed, cons
 int chord_b200_contiguous(const void* x, const int32_t* packed, const void* scale,
                           const int32_t* m_indices, void* out, int32_t* locks, int64_t num_locks,
                           void* workspace, int64_t workspace_bytes, int32_t* status, int64_t m,
-                          int64_t n, int64_t k, int64_t num_experts, void* stream) {
+                          int64_t n, int64_t k, int64_t num_experts, int enable_pdl, void* stream) {
   CHORD_REQUIRE(m > 0 && m % 128 == 0,
                 "contiguous m=%lld must be a positive multiple of 128 (per-expert padded)",
                 static_cast<long long>(m));
@@ -577,9 +592,13 @@ int chord_b200_contiguous(const void* x, const int32_t* packed, const void* scal
                 "contiguous supports at most %d rows and %d experts", chord::kMaxMTiles * 128, 0x7FFF);
   // Token tiles are 128-row blocks, merged in pairs where two neighbours belong to one
   // expert (option contiguous_tile = 128 switches the merging off).
-  p.tile_tokens = chord::options().contiguous_tile == 128 ? 128 : 256;
+  {
+    chord::OptionsReadLock options_guard(chord::options_mutex());
+    p.tile_tokens = chord::options().contiguous_tile == 128 ? 128 : 256;
+  }
   p.top_k = 1;
   p.m_blocks = static_cast<int32_t>(m / 128);
+  p.pdl = enable_pdl != 0;
   p.m_indices = m_indices;
   p.x = static_cast<const __nv_bfloat16*>(x);
   p.out = static_cast<__nv_bfloat16*>(out);
@@ -593,7 +612,7 @@ int chord_b200_masked(const void* x, const int32_t* packed, const void* scale,
                       const int32_t* masked_m, void* out, int32_t* locks, int64_t num_locks,
                       void* workspace, int64_t workspace_bytes, int32_t* status,
                       int64_t num_groups, int64_t max_m, int64_t n, int64_t k, int64_t tile_m,
-                      void* stream) {
+                      int enable_pdl, void* stream) {
   CHORD_REQUIRE(num_groups > 0 && num_groups <= chord::kMaxGroups,
                 "num_groups=%lld must be in [1, %d]", static_cast<long long>(num_groups),
                 chord::kMaxGroups);
@@ -612,6 +631,7 @@ int chord_b200_masked(const void* x, const int32_t* packed, const void* scale,
   p.tile_tokens = static_cast<int32_t>(tile_m);
   p.top_k = 1;
   p.max_m = static_cast<int32_t>(max_m);
+  p.pdl = enable_pdl != 0;
   p.masked_m = masked_m;
   p.x = static_cast<const __nv_bfloat16*>(x);
   p.out = static_cast<__nv_bfloat16*>(out);

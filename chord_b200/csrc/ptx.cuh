@@ -35,6 +35,22 @@ __device__ __forceinline__ bool elect_one() {
   return pred != 0;
 }
 
+// ------------------------------------------- programmatic dependent launch --
+
+// Blocks until every kernel this launch depends on has completed and its writes are
+// visible.  Returns at once in a kernel launched without the programmatic
+// stream-serialization attribute.  Everything before it may only touch what no earlier
+// kernel in the stream writes (shared and tensor memory, the weights).
+__device__ __forceinline__ void grid_dependency_wait() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
+// Lets the next kernel in the stream (if it was launched with the attribute) become
+// resident as SMs free up, instead of after this grid has drained.
+__device__ __forceinline__ void grid_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
 // ---------------------------------------------------------------- mbarrier --
 
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
@@ -117,7 +133,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // out of line so that the hot loops stay short.
 constexpr long long kWaitTimeoutCycles = 4000000000ll;
 
-__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity,
+static __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity,
                                             volatile uint32_t* abort_flag) {
   // A few immediate retries for waits that are about to end, then sleep between
   // tries: some twenty warps per CTA wait most of the time, and a polling loop that
@@ -156,25 +172,26 @@ __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity,
   return __all_sync(__activemask(), ok);
 }
 
-// Bounded wait built on the single-instruction try_wait alone (a failed try has already
-// parked the warp for microseconds, so the loop needs neither a sleep nor a clock, only a
-// try count), with a sticky failure word instead of a result to branch on: `bad` stays 0 while every wait so far was satisfied and becomes 1 when one gives up
-// (2^19 failed tries, or the CTA's abort flag seen non-zero, or `bad` already set on
-// entry and the first two tries failing).  A failed try has suspended the warp until the
-// phase completed or some microseconds passed, so the second try usually succeeds: the
-// abort flag is looked at only after it.  A wait that gives up also raises the abort flag.
-// The loop lives in one asm statement, so that the satisfied case is the try and one
-// branch, with no compiler-visible control flow around it; the caller tests `bad` where
-// it is cheap (once per stage), not after every wait.
+// Bounded wait built on the single-instruction try_wait (a failed try has already
+// parked the warp until the phase completed or an implementation-defined time passed,
+// so the loop needs no sleep), with a sticky failure word instead of a result to
+// branch on: `bad` stays 0 while every wait so far was satisfied and becomes 1 when one
+// gives up.  A wait gives up when 4e9 cycles of SM clock (kWaitTimeoutCycles) have passed since its
+// first failed try, when the CTA's abort flag is seen non-zero, or when `bad` was
+// already set on entry and the first two tries fail; it then also raises the abort
+// flag.  The loop lives in one asm statement, so that the satisfied case is the try and
+// one branch, with no compiler-visible control flow around it; the caller tests `bad`
+// where it is cheap (once per stage), not after every wait.
 __device__ __forceinline__ void mbar_wait_sticky(uint32_t bar, uint32_t parity, uint32_t abort_addr,
-                                                      uint32_t& bad) {
+                                                 uint32_t& bad) {
   asm volatile(
       "{\n\t"
       ".reg .pred p, q;\n\t"
-      ".reg .u32 n, f;\n\t"
+      ".reg .u32 f;\n\t"
+      ".reg .u64 c0, c1;\n\t"
       "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
       "@p bra WAIT_DONE;\n\t"
-      "mov.u32 n, 0;\n\t"
+      "mov.u64 c0, %%clock64;\n\t"
       "WAIT_RETRY:\n\t"
       "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
       "@p bra WAIT_DONE;\n\t"
@@ -182,8 +199,9 @@ __device__ __forceinline__ void mbar_wait_sticky(uint32_t bar, uint32_t parity, 
       "or.b32 f, f, %0;\n\t"
       "setp.ne.u32 q, f, 0;\n\t"
       "@q bra WAIT_FAIL;\n\t"
-      "add.u32 n, n, 1;\n\t"
-      "setp.lt.u32 q, n, 524288;\n\t"
+      "mov.u64 c1, %%clock64;\n\t"
+      "sub.u64 c1, c1, c0;\n\t"
+      "setp.lt.u64 q, c1, 4000000000;\n\t"
       "@q bra WAIT_RETRY;\n\t"
       "WAIT_FAIL:\n\t"
       "mov.u32 %0, 1;\n\t"

@@ -29,10 +29,6 @@
 
 #include "w4a16_gemm.cuh"
 
-#ifndef DEC_ABLATE
-#define DEC_ABLATE 0
-#endif
-
 namespace chord {
 
 constexpr int kDecStepK = 64;                        // K elements per step (one operand slot, four MMAs)
@@ -66,8 +62,6 @@ struct __align__(16) DecodeShared {
   int32_t group_prefix[kMaxGroups + 1];  // masked: first M tile of each group
 };
 
-__device__ __forceinline__ bool z_keep(uint32_t a, uint32_t b) { return a == 0x13572468u && b == 0x24681357u; }
-
 // Bytes of one ring stage: the activation rows of both 64-wide K halves first
 // (1024-aligned for the swizzle), then packed weights and scales.
 __host__ __device__ inline uint32_t decode_stage_bytes(int mma_n) {
@@ -79,21 +73,6 @@ __host__ __device__ inline uint32_t decode_stage_bytes(int mma_n) {
 // which is the common case at decode sizes whatever block size the routing was
 // aligned to.  A tile without any row is not valid (nothing to compute).  Must be
 // called by all 32 lanes of a warp.
-#ifdef CHORD_TIMELINE
-__device__ __forceinline__ unsigned long long dec_globaltimer() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-  return t;
-}
-#define DEC_STAMP(i, cond) do { if (p.profile && (cond)) p.profile[blockIdx.x * 64 + (i)] = dec_globaltimer(); } while (0)
-#define DEC_STAMP_DECL() bool stamped = false
-#define DEC_STAMPED() stamped = true
-#else
-#define DEC_STAMP(i, cond) do {} while (0)
-#define DEC_STAMP_DECL() do {} while (0)
-#define DEC_STAMPED() do {} while (0)
-#endif
-
 __device__ __forceinline__ TileInfo decode_tile_small(const GemmParams& p, const int32_t* group_prefix,
                                                       int32_t tile) {
   TileInfo t;
@@ -173,20 +152,21 @@ struct StepStream {
 // worker's other three warps; a stream-K slice does (lock, partials), and only then do
 // the four warps meet at named barriers.  Kept out of line: it runs once per tile, and
 // inlined into the dequantisation loop it took registers from that loop.
-__device__ __noinline__ void decode_drain(uint32_t d_addr, __nv_bfloat16* out_tile, int32_t ldn,
+static __device__ __noinline__ void decode_drain(uint32_t d_addr, __nv_bfloat16* out_tile, int32_t ldn,
                                           int32_t rows, int32_t mma_n, int32_t seg_type, int32_t seg_peer,
                                           float* workspace, size_t ws_slot, int32_t worker_id,
-                                          int32_t* locks, int32_t* status, __nv_bfloat16* stage,
-                                          uint32_t bar_id, uint32_t wt, bool ok) {
+                                          int32_t* locks, int32_t lock_spins, int32_t* status,
+                                          __nv_bfloat16* stage, uint32_t bar_id, uint32_t wt, bool ok) {
   const uint32_t lane = threadIdx.x & 31u;
   const uint32_t q = (threadIdx.x >> 5) & 3u;
   ptx::tc_fence_after();
   const bool shared_tile = seg_type != kSegFull;
+  bool lock_ok = true;
   if (shared_tile) {
     if (ok && seg_type == kSegOwner && wt == 0) {
       const int* lock = locks + worker_id;
-      bool lock_ok = false;
-      for (uint32_t spin = 0; spin < (1u << 22); ++spin) {
+      lock_ok = false;
+      for (int32_t spin = 0; spin < lock_spins; ++spin) {
         if (ptx::ld_acquire(lock) >= seg_peer) {
           lock_ok = true;
           break;
@@ -253,10 +233,12 @@ __device__ __noinline__ void decode_drain(uint32_t d_addr, __nv_bfloat16* out_ti
   if (shared_tile) {
     ptx::named_bar_sync(bar_id, 128);  // all four warps' partials are written / read
     if (wt == 0) {
-      // The stream-K handshake is completed even after a failure, so that no other
-      // worker spins on a lock that would never move; the status word tells the host.
+      // A contributor completes the handshake even after a failure, so that no owner
+      // spins on a lock that would never move; the status word tells the host.  An owner
+      // whose wait ran out leaves its word as it is (late contributors would make it
+      // non-zero again behind a reset).
       if (seg_type == kSegContrib) ptx::red_release_add(locks + seg_peer, 1);
-      else locks[worker_id] = 0;
+      else if (lock_ok) locks[worker_id] = 0;
     }
   }
 }
@@ -265,7 +247,6 @@ __global__ void __launch_bounds__(kDecThreads, 1)
 w4a16_decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_s,
                     const GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
-  DEC_STAMP(0, threadIdx.x == 0);
   // Dynamic shared memory, 1024-aligned: one ring per worker, then DecodeShared.
   const uint32_t raw_addr = ptx::smem_u32(smem_raw);
   uint8_t* smem = smem_raw + ((1024u - (raw_addr & 1023u)) & 1023u);
@@ -320,6 +301,9 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
           make_uint4(0, 0, 0, 0);
     }
   }
+  // Up to here nothing an earlier kernel of the stream may still be writing has been
+  // read: with programmatic dependent launch the set-up above overlaps that kernel's tail.
+  ptx::grid_dependency_wait();
   if (threadIdx.x == 0) {
     if (p.mode == kModeMasked) {
       int32_t acc = 0;
@@ -342,8 +326,8 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
   ptx::tc_fence_before();
   __syncthreads();
   ptx::tc_fence_after();
+  ptx::grid_launch_dependents();
 
-  DEC_STAMP(1, threadIdx.x == 0);
   const uint32_t tmem_base = __shfl_sync(0xffffffffu, sh.tmem_base, 0);  // uniform, see `warp`
   const uint32_t abort_addr = ptx::smem_u32(&sh.abort_flag);  // raised by any wait that gives up
   const int32_t tiles = __shfl_sync(0xffffffffu, sh.m_blocks, 0) * (p.n / kBlockN);
@@ -396,7 +380,6 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
     int32_t x_off[8];
     uint32_t active = 0;  // bit b: some lane has a row to fetch in round b
     const __nv_bfloat16* src = p.x;
-    CHORD_PROF_INIT();
     while (bad == 0) {
       while (w_more && w_ahead <= w_lead) {
         bool first = false;
@@ -409,20 +392,16 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
           s_row = wsm.t.expert * (p.k / 32) + wsm.kb * (kDecStageK / 32);
           w_col = wsm.t.n0;
         }
-        CHORD_PROF_T(ft0);
         ptx::mbar_wait_sticky(wempty0 + wcur.s * 8u, wcur.ph ^ 1u, abort_addr, bad);
         if (bad != 0) break;
-        CHORD_PROF_ADD(1, ft0);
-        CHORD_PROF_T(ft1);
         if (lane == 0) {
           const uint32_t st = ring + wcur.s * stage_bytes + x_bytes;
           const uint32_t full = wfull0 + wcur.s * 8u;
-          ptx::mbar_arrive_expect_tx(full, kDecWBytes + ((DEC_ABLATE & 16) ? 0 : kDecSBytes));
+          ptx::mbar_arrive_expect_tx(full, kDecWSBytes);
           ptx::tma_load_2d(st, &tm_w, full, 2 * w_col, w_row);
-          if (!(DEC_ABLATE & 16)) ptx::tma_load_2d(st + kDecWBytes, &tm_s, full, w_col, s_row);
+          ptx::tma_load_2d(st + kDecWBytes, &tm_s, full, w_col, s_row);
         }
         __syncwarp();
-        CHORD_PROF_ADD(2, ft1);
         w_row += kDecStageK / 16;
         s_row += kDecStageK / 32;
         wcur.advance(stages);
@@ -446,16 +425,13 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
         }
         src = p.x + xsm.kb * kDecStageK + piece * 8;
       }
-      CHORD_PROF_T(ft2);
       ptx::mbar_wait_sticky(xempty0 + xcur.s * 8u, xcur.ph ^ 1u, abort_addr, bad);
       if (bad != 0) break;
-      CHORD_PROF_ADD(3, ft2);
-      CHORD_PROF_T(ft3);
       const uint32_t xs = ring + xcur.s * stage_bytes;
       const bool second_half = !(k_tail_half && xsm.kb == k_steps - 1);
 #pragma unroll
       for (int b = 0; b < 8; ++b) {
-        if (!(DEC_ABLATE & 8) && ((active >> b) & 1u) && x_off[b] >= 0) {
+        if (((active >> b) & 1u) && x_off[b] >= 0) {
           const uint32_t dst = xs + dst_off[b & 1] + (b >> 1) * 1024u;
           ptx::cp_async_16(dst, src + x_off[b], true);
           if (second_half) ptx::cp_async_16(dst + x_half_bytes, src + x_off[b] + kDecStepK, true);
@@ -476,7 +452,6 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
       src += kDecStageK;
       xcur.advance(stages);
       --w_ahead;
-      CHORD_PROF_ADD(4, ft3);
     }
     // Publish the last step (also when leaving on a timeout: nothing may stay in
     // flight towards shared memory when the CTA retires).
@@ -484,7 +459,6 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
     ptx::fence_proxy_async();
     __syncwarp();
     if (x_pending && lane == 0) ptx::mbar_arrive(xfull0 + xdone.s * 8u);
-    if (wk == 0) CHORD_PROF_FLUSH(2);
     if (bad != 0 && lane == 0 && p.status) atomicOr(p.status, kStatusProducerTimeout);
     __syncwarp();
   } else if (warp < 8) {
@@ -513,12 +487,10 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
           if (lane == 0 && bad == 0) {
             const uint64_t xdesc = ptx::smem_desc_k_sw128(stage + static_cast<uint32_t>(h) * x_half_bytes);
             const uint32_t a_tm = tmem_base + col0 + slot.s * 32u;
-            if (!(DEC_ABLATE & 1)) {
-              ptx::mma_ts(d_tm, a_tm, xdesc, idesc, acc);
-              ptx::mma_ts(d_tm, a_tm + 8, xdesc + 2, idesc, 1);
-              ptx::mma_ts(d_tm, a_tm + 16, xdesc + 4, idesc, 1);
-              ptx::mma_ts(d_tm, a_tm + 24, xdesc + 6, idesc, 1);
-            }
+            ptx::mma_ts(d_tm, a_tm, xdesc, idesc, acc);
+            ptx::mma_ts(d_tm, a_tm + 8, xdesc + 2, idesc, 1);
+            ptx::mma_ts(d_tm, a_tm + 16, xdesc + 4, idesc, 1);
+            ptx::mma_ts(d_tm, a_tm + 24, xdesc + 6, idesc, 1);
             if (h == halves - 1) ptx::mma_commit(xempty0 + cur.s * 8u);
             ptx::mma_commit(afree0 + slot.s * 8u);
           }
@@ -554,14 +526,12 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
     const uint32_t ring_bytes = stages * stage_bytes;
     uint32_t stage_off = 0, stage_bar = 0, stage_ph = 0, slot_bar = 0, slot_ph = 0;
     uint32_t bad = 0;  // sticky: set by the first bounded wait that gives up
-    CHORD_PROF_INIT();
-    DEC_STAMP_DECL();
     const size_t ws_slot = static_cast<size_t>(kBlockN) * p.mma_n;
 
     auto drain = [&](const Segment& sg, int32_t rows, int32_t n0, uint32_t dcol, int32_t mma_n) {
       decode_drain(tmem_base + ((q * 32u) << 16) + dcol, p.out + n0 + q * 32, p.n, rows, mma_n, sg.type,
-                   sg.peer, p.workspace, ws_slot, worker_id, p.locks, p.status, &ws.stage[q][0][0], bar_id,
-                   wt, bad == 0);
+                   sg.peer, p.workspace, ws_slot, worker_id, p.locks, p.lock_spins, p.status,
+                   &ws.stage[q][0][0], bar_id, wt, bad == 0);
     };
     while (iter.next(seg)) {
       const TileInfo t = decode_tile_small(p, sh.group_prefix, seg.tile);
@@ -577,21 +547,14 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
       // worker's own shared and tensor memory); `bad` is tested once per stage.
       auto step = [&](auto half, uint32_t st, bool release_weights) {
         constexpr int h = decltype(half)::value;
-        CHORD_PROF_T(pt1);
         // four K16 rows of packed words, two K32 groups of scales
         uint2 words[4], scales[2];
-        if (DEC_ABLATE & 4) {
-#pragma unroll
-          for (int i = 0; i < 4; ++i) words[i] = make_uint2(st, lane);
-          scales[0] = scales[1] = make_uint2(lane, st);
-        } else {
         words[0] = ptx::lds64<4096 * h + 0>(st + w_off);
         words[1] = ptx::lds64<4096 * h + 1024>(st + w_off);
         words[2] = ptx::lds64<4096 * h + 2048>(st + w_off);
         words[3] = ptx::lds64<4096 * h + 3072>(st + w_off);
         scales[0] = ptx::lds64<512 * h + 0>(st + s_off);
         scales[1] = ptx::lds64<512 * h + 256>(st + s_off);
-        }
         if (release_weights) {
           // The weight half of the stage goes back to the feeder as soon as its last
           // words are in registers.
@@ -600,16 +563,8 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
         }
         // The operand slot is free once the MMAs of its previous use have completed.
         // Waited for here, before the dequantised values exist.
-        CHORD_PROF_T(pt2);
         const uint32_t afree = afree0 + slot_bar;
         ptx::mbar_wait_sticky(afree, slot_ph ^ 1u, abort_addr, bad);
-        CHORD_PROF_ADD(3, pt2);
-        if (DEC_ABLATE & 2) {
-          // keeps the loads alive without the arithmetic
-          if ((words[0].x ^ words[1].x ^ words[2].x ^ words[3].x ^ words[0].y ^ words[1].y ^ words[2].y ^
-               words[3].y ^ scales[0].x ^ scales[1].x ^ scales[0].y ^ scales[1].y) == 0x12345u)
-            bad = 1;
-        } else {
         uint32_t lo[16], hi[16];
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
@@ -621,16 +576,12 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
         const uint32_t a1_lo = __byte_perm(scales[1].x, 0, 0x1010), a1_hi = __byte_perm(scales[1].x, 0, 0x3232);
         const uint32_t b0_lo = __byte_perm(scales[0].y, 0, 0x1010), b0_hi = __byte_perm(scales[0].y, 0, 0x3232);
         const uint32_t b1_lo = __byte_perm(scales[1].y, 0, 0x1010), b1_hi = __byte_perm(scales[1].y, 0, 0x3232);
-        CHORD_PROF_ADD(2, pt1);
-        CHORD_PROF_T(pt3);
         ptx::tc_fence_after();
         const uint32_t a_addr = a_lane + slot_bar * 4u;  // 32 columns per slot
         ptx::tmem_st_16x128b_x8_scaled(a_addr, lo, a0_lo, a0_hi, a1_lo, a1_hi);
         ptx::tmem_st_16x128b_x8_scaled(a_addr + (16u << 16), hi, b0_lo, b0_hi, b1_lo, b1_hi);
         ptx::tmem_wait_st();
         ptx::tc_fence_before();
-        CHORD_PROF_ADD(4, pt3);
-        }
         __syncwarp();
         ptx::mbar_arrive_lane0(afull0 + slot_bar, lane);
         last_bar = afree;
@@ -653,10 +604,7 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
       if (bad == 0) {
         for (int32_t j = 0; j < n_full; ++j) {
           const uint32_t st = ring + stage_off;
-          CHORD_PROF_T(pt0);
           ptx::mbar_wait_sticky(wfull0 + stage_bar, stage_ph, abort_addr, bad);
-          CHORD_PROF_ADD(1, pt0);
-          DEC_STAMP(2, wt == 0 && wk == 0 && !stamped);
           step(std::integral_constant<int, 0>{}, st, false);
           step(std::integral_constant<int, 1>{}, st, true);
           next_stage();
@@ -668,27 +616,18 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
           next_stage();
         }
         // ---- end of the segment: wait for its last MMAs.
-        CHORD_PROF_T(pe0);
         if (bad == 0) ptx::mbar_wait_sticky(last_bar, last_ph, abort_addr, bad);
-        CHORD_PROF_ADD(6, pe0);
       }
-      DEC_STAMP(3, wt == 0 && wk == 0 && !stamped);
       // Drain the accumulator.  A warp that has given up skips the work but still meets
       // its siblings at the named barriers of a stream-K slice, here and for every
       // segment that follows.
-      CHORD_PROF_T(pe1);
       drain(seg, my_out_row, t.n0, col0 + kDecDCol, t.mma_n);
-      CHORD_PROF_ADD(7, pe1);
-      DEC_STAMP(4, wt == 0 && wk == 0 && !stamped);
-      DEC_STAMPED();
     }
-    if (wk == 0 && q < 2) CHORD_PROF_FLUSH(q);
     if (bad != 0 && lane == 0 && p.status) atomicOr(p.status, kStatusDequantTimeout);
   }
 
   ptx::tc_fence_before();
   __syncthreads();
-  DEC_STAMP(5, threadIdx.x == 0);
   if (warp == 1) {
     ptx::tc_fence_after();
     ptx::tmem_dealloc(tmem_base, kTmemCols);

@@ -65,27 +65,6 @@
 
 #include "ptx.cuh"
 
-#ifdef CHORD_PROFILE
-#define CHORD_ABLATE(bit) ((p.ablate >> (bit)) & 1)
-#define CHORD_PROF_INIT() long long prof_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0}; const long long prof_start = clock64()
-#define CHORD_PROF_T(var) const long long var = clock64()
-#define CHORD_PROF_ADD(i, var) prof_acc[i] += clock64() - var
-#define CHORD_PROF_FLUSH(role)                                                         \
-  do {                                                                                 \
-    if (p.profile != nullptr && lane == 0) {                                           \
-      prof_acc[0] = clock64() - prof_start;                                            \
-      for (int pi = 0; pi < 8; ++pi)                                                   \
-        p.profile[(blockIdx.x * 8 + (role)) * 8 + pi] = static_cast<unsigned long long>(prof_acc[pi]); \
-    }                                                                                  \
-  } while (0)
-#else
-#define CHORD_ABLATE(bit) 0
-#define CHORD_PROF_INIT() do {} while (0)
-#define CHORD_PROF_T(var) do {} while (0)
-#define CHORD_PROF_ADD(i, var) do {} while (0)
-#define CHORD_PROF_FLUSH(role) do {} while (0)
-#endif
-
 namespace chord {
 
 enum GemmMode : int32_t { kModeIndexed = 0, kModeContiguous = 1, kModeMasked = 2 };
@@ -147,6 +126,8 @@ struct GemmParams {
   int32_t ksplit;       // single-issuer layouts: a second issuer takes the second K half of tiles of <= 128 tokens
   int32_t a_stages;     // depth of the TMEM A ring; accumulators start at column 64 * a_stages
   int32_t num_locks;
+  int32_t pdl;          // host side only: launch with the programmatic stream-serialization attribute
+  int32_t lock_spins;   // polls (64 ns apart) a stream-K owner spends on its lock word before it gives up
   const int32_t* sorted_ids;
   const int32_t* expert_ids;
   const int32_t* num_tokens_padded;
@@ -157,8 +138,6 @@ struct GemmParams {
   float* workspace;     // grid * 128 * mma_n floats
   int32_t* locks;
   int32_t* status;
-  unsigned long long* profile;  // CHORD_PROFILE builds only: per-CTA cycle counters
-  int32_t ablate;               // CHORD_PROFILE builds only: skip parts of the work (timing studies)
 };
 
 struct TileInfo {
@@ -524,6 +503,9 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
   for (uint32_t i = threadIdx.x; i < x_stages * x_stage_bytes / 16; i += blockDim.x) {
     reinterpret_cast<uint4*>(smem_x)[i] = make_uint4(0, 0, 0, 0);
   }
+  // Up to here nothing an earlier kernel of the stream may still be writing has been
+  // read: with programmatic dependent launch the set-up above overlaps that kernel's tail.
+  ptx::grid_dependency_wait();
   // Number of M tiles.
   if (p.mode == kModeMasked) {
     if (threadIdx.x == 0) {
@@ -600,6 +582,7 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
   ptx::tc_fence_before();
   __syncthreads();
   ptx::tc_fence_after();
+  ptx::grid_launch_dependents();
 
   const uint32_t tmem_base = __shfl_sync(0xffffffffu, sh.tmem_base, 0);  // uniform, see `warp`
   volatile uint32_t* abort_flag = &sh.abort_flag;
@@ -619,33 +602,23 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
       const int32_t rows_per_expert = weights ? p.k / 16 : p.k / 32;
       StageCursor cur;
       bool ok = true;
-      CHORD_PROF_INIT();
       while (ok && iter.next(seg)) {
         const TileInfo t = decode_tile(p, sh, seg.tile);
         if (!t.valid) continue;
         const int32_t col = weights ? 2 * t.n0 : t.n0;
         int32_t row = t.expert * rows_per_expert + seg.kb * rows_per_stage;
         for (int32_t kb = seg.kb; kb < seg.ke; ++kb) {
-          CHORD_PROF_T(pt0);
           if (!ptx::mbar_wait(ptx::smem_u32(&sh.wempty[cur.s]), cur.ph ^ 1u, abort_flag)) {
             ok = false;
             break;
           }
-          CHORD_PROF_ADD(1, pt0);
-          CHORD_PROF_T(pt1);
           const uint32_t full = ptx::smem_u32(&sh.wfull[cur.s]);
-          if (CHORD_ABLATE(5) && !weights) {
-            ptx::mbar_arrive(full);
-          } else {
-            ptx::mbar_arrive_expect_tx(full, stage_bytes);
-            ptx::tma_load_2d(ptx::smem_u32(ring + cur.s * stage_bytes), map, full, col, row);
-          }
+          ptx::mbar_arrive_expect_tx(full, stage_bytes);
+          ptx::tma_load_2d(ptx::smem_u32(ring + cur.s * stage_bytes), map, full, col, row);
           row += rows_per_stage;
           cur.advance(w_stages);
-          CHORD_PROF_ADD(2, pt1);
         }
       }
-      if (weights) CHORD_PROF_FLUSH(0); else CHORD_PROF_FLUSH(4);
       if (!ok) {
         sh.abort_flag = 1;
         if (p.status) atomicOr(p.status, kStatusProducerTimeout);
@@ -657,7 +630,6 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
     StageCursor cur;
     XSubRing xring;
     bool ok = true;
-    CHORD_PROF_INIT();
     if (p.x_load == kXLoadTiled) {
       // Consecutive rows: one box per 64-wide K half, issued by one thread.
       while (ok && threadIdx.x == 64 && iter.next(seg)) {
@@ -761,10 +733,11 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
       const int32_t depth = x_stages >= 4 ? 2 : 1;
       StageCursor done;
       int32_t pending = 0;
-      while (ok && !CHORD_ABLATE(4) && iter.next(seg)) {
+      // A warp whose bounded wait ran out stops copying but keeps walking the tiles, so
+      // that its sibling never waits alone at the three barriers below.
+      while (iter.next(seg)) {
         const TileInfo t = decode_tile(p, sh, seg.tile);
         if (!t.valid) continue;
-        CHORD_PROF_T(pt9);
         ptx::named_bar_sync(2, kHelperThreads);  // readers of the previous tile's rows are done
         // Element offset of each slot's activation row, or -1 for a slot without a token;
         // x_slots = one past the last slot that carries a token.  Slots beyond it keep
@@ -778,6 +751,7 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
           if (row < p.x_rows) atomicMax(&sh.x_slots, slot + 1);
         }
         ptx::named_bar_sync(2, kHelperThreads);
+        if (!ok) continue;
         const int32_t x_slots = sh.x_slots;
         int32_t k_col = seg.kb * kBlockK + static_cast<int32_t>(ch) * 8;
         // Decode-sized tiles (at most 16 rows with a token): each thread owns at most
@@ -795,21 +769,18 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
           fsrc[b] = p.x + (fval[b] ? off : 0) + k_col;
           fdst[b] = half * x_half_bytes + rr * 128u + ((ch8 ^ (rr & 7u)) << 4);
         }
-        CHORD_PROF_ADD(3, pt9);
         for (int32_t kb = seg.kb; kb < seg.ke; ++kb) {
-          CHORD_PROF_T(pt0);
           if (!ptx::mbar_wait_warp(ptx::smem_u32(&sh.xempty[cur.s]), cur.ph ^ 1u, abort_flag)) {
             ok = false;
+            if (lane == 0) sh.abort_flag = 1;  // the sibling's waits end soon too
             break;
           }
-          CHORD_PROF_ADD(1, pt0);
-          CHORD_PROF_T(pt1);
           const uint32_t xs = ptx::smem_u32(smem_x + cur.s * x_stage_bytes);
           const bool col_ok = k_col + 8 <= p.k;
           if (few_rows) {
 #pragma unroll
             for (int b = 0; b < 4; ++b) {
-              if (fact[b] && !CHORD_ABLATE(3)) ptx::cp_async_16(xs + fdst[b], fsrc[b], fval[b] && col_ok);
+              if (fact[b]) ptx::cp_async_16(xs + fdst[b], fsrc[b], fval[b] && col_ok);
               fsrc[b] += kBlockK;
             }
           } else {
@@ -842,10 +813,8 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
           }
           k_col += kBlockK;
           cur.advance(x_stages);
-          CHORD_PROF_ADD(2, pt1);
         }
       }
-      if (warp == 2) CHORD_PROF_FLUSH(5);
       // Drain: publish what is still in flight (also when leaving on a timeout).
       ptx::cp_async_wait_all();
       __syncwarp();
@@ -871,18 +840,15 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
       XSubRing xring;
       uint32_t it = 0, segc = 0;
       bool ok = true;
-      CHORD_PROF_INIT();
       while (ok && iter.next(seg)) {
         const TileInfo t = decode_tile(p, sh, seg.tile);
         if (!t.valid) continue;
         const uint32_t d = d_bufs == 2 ? (segc & 1u) : 0u;
         const uint32_t dph = d_bufs == 2 ? ((segc >> 1) & 1u) : (segc & 1u);
-        CHORD_PROF_T(pt0);
         if (!ptx::mbar_wait(ptx::smem_u32(&sh.dempty[d]), dph ^ 1u, abort_flag)) {
           ok = false;
           break;
         }
-        CHORD_PROF_ADD(1, pt0);
         ptx::tc_fence_after();
         const uint32_t d_addr = tmem_base + d_col0 + (d * ni + me) * d_cols;
         const uint32_t idesc = ptx::idesc_bf16_f32(kBlockN, static_cast<uint32_t>(t.mma_n));
@@ -892,7 +858,6 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
           if (ksplit) {
             const uint32_t a = acur.s << 1;
             const uint32_t aph = acur.ph;
-            CHORD_PROF_T(pt1);
             uint32_t xslot = cur.s;       // barrier (and, with sub-slots, buffer) of this stage
             uint64_t xd = xdesc, xd_half = xdesc_half;
             const bool pair = subslots && t.mma_n > 128;
@@ -909,18 +874,14 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
               ok = false;
               break;
             }
-            CHORD_PROF_ADD(2, pt1);
             if (p.x_load == kXLoadCpAsync) ptx::fence_proxy_async();
             const uint32_t a_addr = tmem_base + acur.s * kAColsPerStage;
             const bool tail = k_tail_half && kb == k_iters - 1;
             if (me == 0) {
-              CHORD_PROF_T(pt2);
               if (!ptx::mbar_wait(ptx::smem_u32(&sh.afull[a]), aph, abort_flag)) {
                 ok = false;
                 break;
               }
-              CHORD_PROF_ADD(3, pt2);
-              CHORD_PROF_T(pt3);
               ptx::tc_fence_after();
               ptx::mma_ts(d_addr, a_addr, xd, idesc, acc);
               ptx::mma_ts(d_addr, a_addr + 8, xd + 2, idesc, 1);
@@ -928,16 +889,12 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
               ptx::mma_ts(d_addr, a_addr + 24, xd + 6, idesc, 1);
               acc = 1;
               ptx::mma_commit(ptx::smem_u32(&sh.aempty[a]));
-              CHORD_PROF_ADD(4, pt3);
             }
             if (me == 0 ? !split : split) {
-              CHORD_PROF_T(pt4);
               if (!ptx::mbar_wait(ptx::smem_u32(&sh.afull[a + 1]), aph, abort_flag)) {
                 ok = false;
                 break;
               }
-              CHORD_PROF_ADD(3, pt4);
-              CHORD_PROF_T(pt5);
               ptx::tc_fence_after();
               if (!tail) {
                 const uint64_t xd1 = xd + xd_half;
@@ -948,7 +905,6 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
                 acc = 1;
               }
               ptx::mma_commit(ptx::smem_u32(&sh.aempty[a + 1]));
-              CHORD_PROF_ADD(4, pt5);
             }
             // Both issuers account for the activation stage: a commit after MMAs of one's
             // own, a plain arrival otherwise.
@@ -957,40 +913,28 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
           } else if ((it & (ni - 1)) == me) {
             const uint32_t a = acur.s << 1;  // barrier of the first K half; the second is a + 1
             const uint32_t aph = acur.ph;
-            CHORD_PROF_T(pt1);
-            if (!CHORD_ABLATE(4) &&
-                !ptx::mbar_wait(ptx::smem_u32(&sh.xfull[cur.s]), cur.ph, abort_flag)) {
+            if (!ptx::mbar_wait(ptx::smem_u32(&sh.xfull[cur.s]), cur.ph, abort_flag)) {
               ok = false;
               break;
             }
-            CHORD_PROF_ADD(2, pt1);
             if (p.x_load == kXLoadCpAsync) ptx::fence_proxy_async();
-            CHORD_PROF_T(pt2);
             if (!ptx::mbar_wait(ptx::smem_u32(&sh.afull[a]), aph, abort_flag)) {
               ok = false;
               break;
             }
-            CHORD_PROF_ADD(3, pt2);
-            CHORD_PROF_T(pt3);
             ptx::tc_fence_after();
             const uint32_t a_addr = tmem_base + acur.s * kAColsPerStage;
-            if (!CHORD_ABLATE(0)) {
-              ptx::mma_ts(d_addr, a_addr, xdesc, idesc, acc);
-              ptx::mma_ts(d_addr, a_addr + 8, xdesc + 2, idesc, 1);
-              ptx::mma_ts(d_addr, a_addr + 16, xdesc + 4, idesc, 1);
-              ptx::mma_ts(d_addr, a_addr + 24, xdesc + 6, idesc, 1);
-            }
+            ptx::mma_ts(d_addr, a_addr, xdesc, idesc, acc);
+            ptx::mma_ts(d_addr, a_addr + 8, xdesc + 2, idesc, 1);
+            ptx::mma_ts(d_addr, a_addr + 16, xdesc + 4, idesc, 1);
+            ptx::mma_ts(d_addr, a_addr + 24, xdesc + 6, idesc, 1);
             ptx::mma_commit(ptx::smem_u32(&sh.aempty[a]));
-            CHORD_PROF_ADD(4, pt3);
-            CHORD_PROF_T(pt4);
             if (!ptx::mbar_wait(ptx::smem_u32(&sh.afull[a + 1]), aph, abort_flag)) {
               ok = false;
               break;
             }
-            CHORD_PROF_ADD(3, pt4);
-            CHORD_PROF_T(pt5);
             ptx::tc_fence_after();
-            if (!(k_tail_half && kb == k_iters - 1) && !CHORD_ABLATE(0)) {
+            if (!(k_tail_half && kb == k_iters - 1)) {
               const uint64_t xd1 = xdesc + xdesc_half;
               ptx::mma_ts(d_addr, a_addr + 32, xd1, idesc, 1);
               ptx::mma_ts(d_addr, a_addr + 40, xd1 + 2, idesc, 1);
@@ -1000,7 +944,6 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
             acc = 1;
             ptx::mma_commit(ptx::smem_u32(&sh.aempty[a + 1]));
             ptx::mma_commit(ptx::smem_u32(&sh.xempty[cur.s]));
-            CHORD_PROF_ADD(4, pt5);
           }
           xdesc += xdesc_stage;
           cur.advance(x_stages);
@@ -1013,7 +956,6 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
         else ptx::mbar_arrive(ptx::smem_u32(&sh.dfull[d]));
         ++segc;
       }
-      if (me == 0) CHORD_PROF_FLUSH(1);
       if (!ok) {
         sh.abort_flag = 1;
         if (p.status) atomicOr(p.status, kStatusMmaTimeout);
@@ -1066,16 +1008,8 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
         const uint32_t a_hi = __byte_perm(sc.x, 0, 0x3232);
         const uint32_t b_lo = __byte_perm(sc.y, 0, 0x1010);
         const uint32_t b_hi = __byte_perm(sc.y, 0, 0x3232);
-        if (CHORD_ABLATE(1)) {
-#pragma unroll
-          for (int z = 0; z < 4; ++z) {
-            lo[4 * j + z] = words[j].x ^ a_lo;
-            hi[4 * j + z] = words[j].y ^ b_hi;
-          }
-        } else {
-          dequant_word(words[j].x, a_lo, a_hi, lo + 4 * j);
-          dequant_word(words[j].y, b_lo, b_hi, hi + 4 * j);
-        }
+        dequant_word(words[j].x, a_lo, a_hi, lo + 4 * j);
+        dequant_word(words[j].y, b_lo, b_hi, hi + 4 * j);
       }
     };
     // Waits for the slot to be free, then stores one K half: lo to TMEM lanes 0-15 of
@@ -1085,16 +1019,11 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
       if (!ptx::mbar_wait_warp(ptx::smem_u32(&sh.aempty[slot]), aph ^ 1u, abort_flag)) return false;
       ptx::tc_fence_after();
       const uint32_t a_addr = tmem_base + ((q * 32u) << 16) + slot * (kAColsPerStage / 2);
-      if (!CHORD_ABLATE(2)) {
-        ptx::tmem_st_16x128b_x8(a_addr, lo);
-        ptx::tmem_st_16x128b_x8(a_addr + (16u << 16), hi);
-      } else if (lo[3] == 0x12345678u && hi[5] == 0x9abcdef0u) {
-        sh.x_slots = 1;  // keeps the dequantised values alive
-      }
+      ptx::tmem_st_16x128b_x8(a_addr, lo);
+      ptx::tmem_st_16x128b_x8(a_addr + (16u << 16), hi);
       pending = static_cast<int32_t>(slot);
       return true;
     };
-    CHORD_PROF_INIT();
     while (ok && iter.next(seg)) {
       const TileInfo t = decode_tile(p, sh, seg.tile);
       if (!t.valid) continue;
@@ -1116,24 +1045,19 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
                           acur.advance_by(kDequantGroups, a_stages)) {
         const uint32_t a = acur.s << 1;  // half-slots a (first K half) and a + 1 (second)
         const uint32_t aph = acur.ph;
-        CHORD_PROF_T(pt0);
         if (!ptx::mbar_wait_warp(ptx::smem_u32(&sh.wfull[cur.s]), cur.ph, abort_flag)) {
           ok = false;
           break;
         }
-        CHORD_PROF_ADD(1, pt0);
         const uint8_t* wsrc = smem_w + cur.s * kWStageBytes + w_off;
         const uint8_t* ssrc = smem_s + cur.s * kSStageBytes + s_off;
         uint2 words[4], scales[2];
         uint32_t lo[16], hi[16];
-        CHORD_PROF_T(pt1);
         load_half(wsrc, ssrc, 0, words, scales);
         dequant_half(words, scales, lo, hi);
         // Second half's words are fetched before the first half is stored, and the
         // stage goes back to the producers as soon as they are in registers.
         load_half(wsrc, ssrc, 1, words, scales);
-        CHORD_PROF_ADD(2, pt1);
-        CHORD_PROF_T(pt2);
         publish();  // previous stage's second half
         __syncwarp();
         if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&sh.wempty[cur.s]));
@@ -1141,17 +1065,12 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
           ok = false;
           break;
         }
-        CHORD_PROF_ADD(3, pt2);
-        CHORD_PROF_T(pt3);
         dequant_half(words, scales, lo, hi);
-        CHORD_PROF_ADD(2, pt3);
-        CHORD_PROF_T(pt4);
         publish();  // this stage's first half
         if (!store_half(a + 1, aph, lo, hi)) {
           ok = false;
           break;
         }
-        CHORD_PROF_ADD(4, pt4);
       }
       // `it` overshoots the segment's end by less than one stride: bring the cursor back.
       if (ok) {
@@ -1164,7 +1083,6 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
       }
     }
     publish();
-    if (warp == kFirstDequantWarp) CHORD_PROF_FLUSH(2);
     if (!ok && lane == 0) {
       sh.abort_flag = 1;
       if (p.status) atomicOr(p.status, kStatusDequantTimeout);
@@ -1175,7 +1093,6 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
     const uint32_t et = threadIdx.x - kFirstEpilogueWarp * 32;  // 0..127 == TMEM lane
     uint32_t segc = 0, it0 = 0;
     bool ok = true;
-    CHORD_PROF_INIT();
     const size_t ws_slot = static_cast<size_t>(kBlockN) * p.mma_n;
     while (ok && iter.next(seg)) {
       const TileInfo t = decode_tile(p, sh, seg.tile);
@@ -1185,11 +1102,12 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
       ptx::named_bar_sync(1, 128);  // previous segment's out_row readers are done
       const int32_t row_slots = (t.rows + 15) & ~15;  // >= t.mma_n; beyond it: rows written as zeros
       for (int32_t c = et; c < row_slots; c += 128) sh.out_row[c] = out_row_of(p, t, c);
+      bool lock_ok = true;
       if (seg.type == kSegOwner && et == 0) {
         // Wait (bounded) until every other slice of this tile has published its partial.
         const int* lock = p.locks + blockIdx.x;
-        bool lock_ok = false;
-        for (uint32_t spin = 0; spin < (1u << 22); ++spin) {
+        lock_ok = false;
+        for (int32_t spin = 0; spin < p.lock_spins; ++spin) {
           if (ptx::ld_acquire(lock) >= seg.peer) {
             lock_ok = true;
             break;
@@ -1200,7 +1118,6 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
       }
       // The four warps must agree on the outcome before any of them leaves the loop,
       // or the named barriers below would wait for warps that are gone.
-      CHORD_PROF_T(pt0);
       if (!ptx::mbar_wait_warp(ptx::smem_u32(&sh.dfull[d]), dph, abort_flag) && lane == 0) {
         sh.epilogue_failed = 1;
       }
@@ -1210,8 +1127,6 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
         ok = false;
         break;
       }
-      CHORD_PROF_ADD(1, pt0);
-      CHORD_PROF_T(pt1);
       const uint32_t d_addr = tmem_base + ((q * 32u) << 16) + d_col0 + d * ni * d_cols;
       __nv_bfloat16* out_tile = p.out + t.n0 + q * 32;
       // Issuer i accumulated the stages it0 + j with (it0 + j) % ni == i; it took part
@@ -1282,13 +1197,14 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
         if (et == 0) ptx::red_release_add(p.locks + seg.peer, 1);
       } else if (seg.type == kSegOwner) {
         ptx::named_bar_sync(1, 128);
-        if (et == 0) p.locks[blockIdx.x] = 0;
+        // After a timeout the word is left as it is: contributors that arrive late would
+        // otherwise leave it non-zero behind a reset, and the caller has to clear the
+        // buffer anyway once the status word reports the failure.
+        if (et == 0 && lock_ok) p.locks[blockIdx.x] = 0;
       }
-      CHORD_PROF_ADD(2, pt1);
       ++segc;
       it0 += seg_len;
     }
-    if (warp == kFirstEpilogueWarp) CHORD_PROF_FLUSH(3);
     if (!ok && lane == 0) {
       sh.abort_flag = 1;
       if (p.status) atomicOr(p.status, kStatusEpilogueTimeout);

@@ -6,37 +6,69 @@ from __future__ import annotations
 
 import torch
 
-from . import _lib
-from .packing import PreparedWeight, _validate_supported_architecture
+from . import _checks, _lib
+from .packing import PreparedWeight
 
 MAX_BLOCK_M = 256
 
-# Scratch the binder owns, per (device, stream): a zeroed lock buffer for calls
-# that pass locks=None, and one status word per device.
+# Scratch the binder owns: per (device, stream) a zeroed lock buffer for calls that
+# pass locks=None, and one status word per device.
 _DEFAULT_LOCKS: dict[tuple[int, int], torch.Tensor] = {}
 _STATUS: dict[int, torch.Tensor] = {}
+
+_STATUS_BITS = {1: "producer wait", 2: "MMA-issuer wait", 4: "dequantisation wait",
+                8: "epilogue wait", 16: "stream-K lock wait"}
 
 
 def _device_index(device: torch.device) -> int:
     return device.index if device.index is not None else torch.cuda.current_device()
 
 
+def _refuse_allocation_in_capture(device: torch.device, what: str) -> None:
+    """A buffer created inside a stream capture would come from the graph's private
+    pool and be handed out again after the graph is gone."""
+    if torch.cuda.is_current_stream_capturing():
+        raise RuntimeError(
+            f"{what} would have to be allocated inside a CUDA-graph capture; "
+            "pass your own zeroed locks tensor to captured calls and run one call on "
+            f"{device} before capturing")
+
+
 def status_word(device: torch.device) -> torch.Tensor:
     """Device word a kernel ORs an error code into when it gives up on a bounded
-    wait (instead of hanging).  Zero in normal operation; read it after a
-    synchronize when debugging."""
+    wait (instead of hanging).  Zero in normal operation; :func:`check_status` reads it."""
     index = _device_index(device)
     word = _STATUS.get(index)
     if word is None:
+        _refuse_allocation_in_capture(device, "the status word")
         word = torch.zeros(1, dtype=torch.int32, device=device)
         _STATUS[index] = word
     return word
+
+
+def check_status(device=None) -> None:
+    """Synchronise ``device`` and raise ``RuntimeError`` if any kernel since the last
+    check gave up on a bounded wait (its output is then not to be trusted).  Clears the
+    word.  After a stream-K lock timeout the caller's ``locks`` tensor must be zeroed
+    again before it is reused."""
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    word = _STATUS.get(_device_index(device))
+    if word is None:
+        return
+    torch.cuda.synchronize(device)
+    bits = int(word.item())
+    if bits:
+        word.zero_()
+        names = [name for bit, name in _STATUS_BITS.items() if bits & bit]
+        raise RuntimeError(f"a chord_b200 kernel gave up on a bounded wait ({', '.join(names)}; "
+                           f"status {bits})")
 
 
 def default_locks(device: torch.device) -> torch.Tensor:
     key = (_device_index(device), torch.cuda.current_stream(device).cuda_stream)
     locks = _DEFAULT_LOCKS.get(key)
     if locks is None:
+        _refuse_allocation_in_capture(device, "the default locks buffer (locks=None)")
         locks = torch.zeros(1024, dtype=torch.int32, device=device)
         _DEFAULT_LOCKS[key] = locks
     return locks
@@ -66,82 +98,13 @@ def gemm_scratch(device: torch.device, tile_tokens: int, locks: torch.Tensor | N
     return locks, workspace, ws_bytes
 
 
-def _check_cuda_int32(name: str, tensor: torch.Tensor, device: torch.device) -> None:
-    if not isinstance(tensor, torch.Tensor):
-        raise TypeError(f"{name} must be a torch.Tensor, got {type(tensor).__name__}")
-    if tensor.dtype != torch.int32:
-        raise TypeError(f"{name} must be torch.int32, got {tensor.dtype}")
-    if tensor.device != device or not tensor.is_contiguous():
-        raise ValueError(f"{name} must be contiguous and on {device}")
-
-
-def _validate_prepared_weight(weight: PreparedWeight, device: torch.device):
-    """Same checks as chord_kernels/operator/api.py:233-248."""
-    if not isinstance(weight, PreparedWeight):
-        raise TypeError("weight must be a PreparedWeight from pack_w4a16()")
-    n, k, e = weight.n, weight.k, weight.num_experts
-    packed, scale = weight.packed, weight.scale
-    if packed.dtype != torch.int32 or tuple(packed.shape) != (e, k // 16, n * 2):
-        raise ValueError(f"packed weight must be int32 {(e, k // 16, n * 2)}, got {tuple(packed.shape)}")
-    if scale.dtype != torch.bfloat16 or tuple(scale.shape) != (e, k // 32, n):
-        raise ValueError(f"packed scale must be BF16 {(e, k // 32, n)}, got {tuple(scale.shape)}")
-    if packed.device != device or scale.device != device:
-        raise ValueError(f"weight must be on {device}, got {packed.device}")
-    if not packed.is_contiguous() or not scale.is_contiguous():
-        raise ValueError("packed weight and scale must be contiguous")
-    return packed, scale, e, n, k
-
-
-def _validate_routing(sorted_ids, expert_ids, num_tokens_padded, block_m, routed_limit, num_experts):
-    """Synchronizing check of the routing contract (``validate_routing=True``);
-    same rules and messages as chord_kernels/operator/api.py:251-297."""
-    padded_count = int(num_tokens_padded.reshape(-1)[0].item())
-    if padded_count < 0 or padded_count > sorted_ids.numel():
-        raise ValueError(
-            f"num_tokens_padded must be in [0, {sorted_ids.numel()}], got {padded_count}"
-        )
-    if padded_count % block_m:
-        raise ValueError(
-            f"num_tokens_padded must be a multiple of block_m={block_m}, got {padded_count}"
-        )
-    active_blocks = padded_count // block_m
-    if expert_ids.numel() < active_blocks:
-        raise ValueError(
-            f"expert_ids must cover {active_blocks} active blocks, got {expert_ids.numel()}"
-        )
-    if not padded_count:
-        return
-    ids = sorted_ids[:padded_count]
-    experts = expert_ids[:active_blocks]
-    valid = ids.view(-1, block_m) < routed_limit
-    route_ids = torch.sort(ids[(ids >= 0) & (ids < routed_limit)]).values
-    if route_ids.numel() > 1:
-        unique = bool((route_ids[1:] != route_ids[:-1]).all().item())
-    else:
-        unique = True
-    if not bool((ids >= 0).all().item()):
-        raise ValueError("sorted_ids values must be non-negative")
-    if bool((valid & ((~valid).cumsum(dim=1) > 0)).any().item()):
-        raise ValueError(
-            "each active sorted_ids block must hold its routed ids as a prefix "
-            "followed only by sentinels"
-        )
-    if not bool(((experts >= 0) & (experts < num_experts)).all().item()):
-        raise ValueError(f"expert_ids values must be in [0, {num_experts - 1}]")
-    if not unique:
-        raise ValueError("active sorted_ids contains duplicate routed ids")
-
-
 def select_block_m(shape_n: int, shape_k: int, num_experts: int, routed_m: int) -> int:
     """Routing block size for a call; a multiple of 8 (here always a multiple of 16:
     the token dimension of a tile is the MMA's N, whose minimum is 16)."""
-    for name, value in (("shape_n", shape_n), ("shape_k", shape_k), ("num_experts", num_experts)):
-        if isinstance(value, bool) or not isinstance(value, int) or value <= 0:
-            raise ValueError(f"{name} must be a positive int, got {value!r}")
-    if isinstance(routed_m, bool) or not isinstance(routed_m, int):
-        raise TypeError(f"routed_m must be an int, got {type(routed_m).__name__}")
-    if routed_m < 0:
-        raise ValueError(f"routed_m must be non-negative, got {routed_m}")
+    _checks.integer("shape_n", shape_n, minimum=1)
+    _checks.integer("shape_k", shape_k, minimum=1)
+    _checks.integer("num_experts", num_experts, minimum=1)
+    _checks.integer("routed_m", routed_m, minimum=0, type_error=True)
     return int(_lib.load().chord_b200_indexed_block_m(shape_n, shape_k, num_experts, routed_m))
 
 
@@ -189,48 +152,30 @@ def w4a16_indexed(
     """
     if not isinstance(inputs, torch.Tensor) or inputs.ndim != 2 or inputs.dtype != torch.bfloat16:
         raise TypeError("inputs must be a 2D torch.bfloat16 tensor")
-    if not inputs.is_cuda or not inputs.is_contiguous() or 0 in inputs.shape:
-        raise ValueError("inputs must be a non-empty contiguous CUDA tensor")
+    _checks.tensor("inputs", inputs, nonempty=True)
     device = inputs.device
-    _validate_supported_architecture(device)
-    packed, scale, num_experts, shape_n, shape_k = _validate_prepared_weight(weight, device)
+    _checks.supported_gpu(device)
+    packed, scale, num_experts, shape_n, shape_k = _checks.prepared_weight(weight, device)
     if inputs.size(1) != shape_k:
         raise ValueError(f"inputs K={inputs.size(1)} does not match the weight's K={shape_k}")
-    for name, tensor in (("sorted_ids", sorted_ids), ("expert_ids", expert_ids),
-                         ("num_tokens_padded", num_tokens_padded)):
-        _check_cuda_int32(name, tensor, device)
-    if sorted_ids.ndim != 1 or expert_ids.ndim != 1:
-        raise ValueError("sorted_ids and expert_ids must be 1D")
+    _checks.tensor("sorted_ids", sorted_ids, dtype=torch.int32, ndim=1, device=device)
+    _checks.tensor("expert_ids", expert_ids, dtype=torch.int32, ndim=1, device=device)
+    _checks.tensor("num_tokens_padded", num_tokens_padded, dtype=torch.int32, device=device)
     if num_tokens_padded.numel() != 1 or num_tokens_padded.ndim > 1:
         raise ValueError("num_tokens_padded must be a scalar or a one-element tensor")
-    if isinstance(top_k, bool) or not isinstance(top_k, int) or top_k <= 0:
-        raise ValueError(f"top_k must be a positive int, got {top_k!r}")
-
+    _checks.integer("top_k", top_k, minimum=1)
     routed_m = inputs.size(0) * top_k
-    if block_m is None:
-        block_m = select_block_m(shape_n, shape_k, num_experts, routed_m)
-    elif isinstance(block_m, bool) or not isinstance(block_m, int) or block_m <= 0 or block_m % 8:
-        raise ValueError(f"routing block_m must be a positive multiple of 8, got {block_m!r}")
-    elif block_m > MAX_BLOCK_M:
-        raise ValueError(f"routing block_m must be at most {MAX_BLOCK_M}, got {block_m}")
-
+    block_m = (select_block_m(shape_n, shape_k, num_experts, routed_m) if block_m is None
+               else _checks.routing_block_m(block_m, MAX_BLOCK_M))
     if locks is not None:
-        _check_cuda_int32("locks", locks, device)
-        if locks.ndim != 1:
-            raise ValueError("locks must be 1D")
+        _checks.tensor("locks", locks, dtype=torch.int32, ndim=1, device=device)
     if outputs is None:
         outputs = torch.empty((routed_m, shape_n), dtype=torch.bfloat16, device=device)
     else:
-        if not isinstance(outputs, torch.Tensor) or outputs.dtype != torch.bfloat16:
-            raise TypeError("outputs must be a torch.bfloat16 tensor")
-        if (tuple(outputs.shape) != (routed_m, shape_n) or outputs.device != device
-                or not outputs.is_contiguous()):
-            raise ValueError(
-                f"outputs must be contiguous BF16 {(routed_m, shape_n)} on {device}, "
-                f"got {tuple(outputs.shape)}"
-            )
+        _checks.bf16_output(outputs, (routed_m, shape_n), device, exact_shape=True)
     if validate_routing:
-        _validate_routing(sorted_ids, expert_ids, num_tokens_padded, block_m, routed_m, num_experts)
+        _checks.routing_contract(sorted_ids, expert_ids, num_tokens_padded, block_m, routed_m,
+                                 num_experts)
 
     lib = _lib.load()
     with torch.cuda.device(device):
@@ -279,4 +224,4 @@ def indexed(
     )
 
 
-__all__ = ["indexed", "indexed_block_m", "w4a16_indexed", "select_block_m", "status_word"]
+__all__ = ["check_status", "indexed", "indexed_block_m", "w4a16_indexed", "select_block_m", "status_word"]

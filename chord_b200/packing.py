@@ -8,19 +8,7 @@ from collections.abc import Iterator
 
 import torch
 
-from . import _lib
-
-SUPPORTED_COMPUTE_CAPABILITY_MAJOR = 10
-
-
-def _validate_supported_architecture(device: torch.device) -> None:
-    """Counterpart of packing.py:16-23; this build runs on compute capability 10.x only."""
-    capability = torch.cuda.get_device_capability(device)
-    if capability[0] != SUPPORTED_COMPUTE_CAPABILITY_MAJOR:
-        raise RuntimeError(
-            "chord_b200 W4A16 kernels require an SM100/SM103 Blackwell GPU, got compute "
-            f"capability {capability[0]}.{capability[1]} on {device}"
-        )
+from . import _checks, _lib
 
 
 @dataclasses.dataclass(frozen=True, eq=False)
@@ -56,38 +44,27 @@ def pack_w4a16(
     BF16 ``[E, N, K/32]``.  Argument checks and exception classes follow
     packing.py:68-117.
     """
-    if not isinstance(packed, bool):
-        raise TypeError(f"packed must be a bool, got {type(packed).__name__}")
-    if not isinstance(weight_uint4, torch.Tensor):
-        raise TypeError(f"weight_uint4 must be a torch.Tensor, got {type(weight_uint4).__name__}")
-    if not isinstance(weight_scale, torch.Tensor):
-        raise TypeError(f"weight_scale must be a torch.Tensor, got {type(weight_scale).__name__}")
+    _checks.flag("packed", packed)
+    layout = "[E, N, K/8]" if packed else "[E, N, K]"
+    weight_uint4 = _checks.tensor("weight_uint4", weight_uint4, dtype=torch.int32, cuda=False,
+                                  contiguous=False)
+    _checks.tensor("weight_scale", weight_scale, cuda=False, contiguous=False)
     if weight_uint4.ndim != 3:
-        expected = "[E, N, K/8]" if packed else "[E, N, K]"
-        raise ValueError(f"weight_uint4 must have shape {expected}, got {weight_uint4.shape}")
-    if weight_uint4.dtype != torch.int32:
-        raise TypeError(f"weight_uint4 must be torch.int32, got {weight_uint4.dtype}")
+        raise ValueError(f"weight_uint4 must have shape {layout}, got {tuple(weight_uint4.shape)}")
     if not weight_uint4.is_cuda or not weight_uint4.is_contiguous():
         raise ValueError("weight_uint4 must be a contiguous CUDA tensor")
-    _validate_supported_architecture(weight_uint4.device)
-
-    num_experts, shape_n, stored_shape_k = weight_uint4.shape
-    if num_experts == 0 or shape_n == 0 or stored_shape_k == 0:
+    _checks.supported_gpu(weight_uint4.device)
+    num_experts, shape_n, stored_k = weight_uint4.shape
+    if 0 in (num_experts, shape_n, stored_k):
         raise ValueError(f"weight_uint4 dimensions must be non-zero, got {tuple(weight_uint4.shape)}")
-    shape_k = stored_shape_k * 8 if packed else stored_shape_k
-    expected_scale_shape = (num_experts, shape_n, shape_k // 32)
-    if shape_n % 128 != 0:
-        raise ValueError(f"shape_n must be divisible by 128, got {shape_n}")
-    if shape_k % 64 != 0:
-        raise ValueError(f"shape_k must be divisible by 64, got {shape_k}")
-    if tuple(weight_scale.shape) != expected_scale_shape:
-        raise ValueError(
-            f"weight_scale must have shape {expected_scale_shape}, got {tuple(weight_scale.shape)}"
-        )
-    if weight_scale.dtype != torch.bfloat16:
-        raise TypeError(f"weight_scale must be torch.bfloat16, got {weight_scale.dtype}")
-    if weight_scale.device != weight_uint4.device or not weight_scale.is_contiguous():
-        raise ValueError("weight_scale must be contiguous and on the weight device")
+    shape_k = stored_k * (8 if packed else 1)
+    for name, extent, unit in (("shape_n", shape_n, 128), ("shape_k", shape_k, 64)):
+        if extent % unit:
+            raise ValueError(f"{name} must be divisible by {unit}, got {extent}")
+    scale_shape = (num_experts, shape_n, shape_k // 32)
+    if tuple(weight_scale.shape) != scale_shape:
+        raise ValueError(f"weight_scale must have shape {scale_shape}, got {tuple(weight_scale.shape)}")
+    _checks.tensor("weight_scale", weight_scale, dtype=torch.bfloat16, device=weight_uint4.device)
 
     lib = _lib.load()
     device = weight_uint4.device

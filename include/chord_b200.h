@@ -18,7 +18,10 @@
  *    (bindings raise ValueError), 2 for an unsupported GPU and 3 for a CUDA
  *    failure (bindings raise RuntimeError).  chord_b200_last_error() returns
  *    the message of the calling thread's last failure.
- *  - Entry points are re-entrant and thread-safe.
+ *  - Entry points may be called from several host threads.  The options set by
+ *    chord_b200_set_option() are process-wide: a launch reads them under a lock and
+ *    sees one consistent set, but which set a launch racing with a set_option call
+ *    sees is unspecified.
  *  - Data formats (bit-exact with the reference):
  *      packed weight int32 [E, K/16, 2N], scale bf16 [E, K/32, N] as produced
  *      by pack_w4a16 (chord_kernels/operator/packing.py:55-138,
@@ -40,11 +43,30 @@ const char* chord_b200_last_error(void);
 /* Library build tag, e.g. "chord_b200 sm_100a". */
 const char* chord_b200_version(void);
 
-/* Tuning knobs for sweeps: "x_load" (routed-row gather of `indexed`: 0 cp.async
- * helper warps, 1 TMA tile::gather4),
- * "dequant_groups" (2 or 4), "max_stages" (0 = auto), "grid_limit" (0 = one
- * CTA per SM).  Counterpart of the reference's CHORD_W4A16_* environment
- * overrides (chord_kernels/operator/grouped/heuristics.py:32-39).  Process-wide. */
+/* Process-wide tuning knobs, the counterpart of the reference's CHORD_W4A16_*
+ * environment overrides (chord_kernels/operator/grouped/heuristics.py:32-39).
+ * Unknown names and out-of-range values return 1.
+ *   "x_load"          routed-row gather of `indexed` in the general kernel: 0 cp.async
+ *                     helper warps (default), 1 TMA tile::gather4
+ *   "dequant_groups"  2 (default) or 4 groups of four dequantising warps
+ *   "issuers"         0 automatic (default); 1, 2 or 4 MMA-issuing threads
+ *   "contiguous_tile" 0 / 256 merge neighbouring 128-row blocks of one expert
+ *                     (default), 128 do not
+ *   "a_stages"        0 automatic (default); 2..7 depth of the tensor-memory operand ring
+ *   "pregather"       1 (default) `indexed` with blocks of 64 rows or more first copies
+ *                     the routed rows into slot order; 0 gathers inside the kernel
+ *   "ksplit"          1 (default) single-issuer layouts give the second K half of tiles
+ *                     of at most 128 tokens to a second issuer; 0 off
+ *   "decode_kernel"   1 (default) token tiles of at most 32 rows (indexed, masked) run
+ *                     the warpgroup-per-worker kernel; 0 always the general kernel
+ *   "max_stages"      0 as many shared-memory stages as fit (default), else a cap
+ *   "grid_limit"      0 one CTA per SM (default), else at most this many CTAs
+ *   "pdl"             1 launches of `indexed` and the SiLU*mul kernels carry the
+ *                     programmatic stream-serialization attribute (programmatic
+ *                     dependent launch, as the reference's enable_pdl does for its
+ *                     grouped operators, launcher.cpp:440-451); 0 (default) off
+ *   "lock_spins"      polls, 64 ns apart, a stream-K owner spends on its lock word
+ *                     before it gives up and reports through `status` (default 2^22) */
 int chord_b200_set_option(const char* name, int64_t value);
 
 /* ---- packing: replaces repack_w4a16<kPacked> (repack.cuh:48-121) ----------
@@ -133,6 +155,14 @@ int chord_b200_indexed(const void* x, const int32_t* packed, const void* scale,
  * allocation is forbidden.
  *  - Limits: block_m <= 64 and at most 160 CTAs (one per SM); anything larger is
  *    refused with return code 1 and a message naming the limit.
+ *  - Which kernel runs follows from what fits into the 5 MiB: with block_m <= 16 the
+ *    decode kernel, as for chord_b200_indexed (results bit-equal to it).  With
+ *    block_m 17..32 the decode kernel's one slot per warpgroup (9.7 MB on 148 SMs) does
+ *    not fit, so the general kernel runs where chord_b200_indexed would run the decode
+ *    kernel: same results within the output tolerance, not bit-equal, and slower.
+ *    With block_m 33..64 there is no room for the slot-ordered copy of the routed
+ *    rows, so they are gathered inside the kernel (slower than chord_b200_indexed
+ *    with its full workspace).
  *  - The first call on each device looks up the array's device address
  *    (cudaGetSymbolAddress, once per device); make that first call outside any
  *    stream capture.
@@ -151,23 +181,29 @@ int chord_b200_indexed_static_scratch(const void* x, const int32_t* packed, cons
 /* ---- contiguous GEMM: replaces launch_grouped_w4a16_contiguous
  * (launcher.cpp:505-549) --------------------------------------------------------
  * out[r, :] = x[r, :] . dequant(W[m_indices[tile first row]])^T for every 128-row
- * tile whose first row has m_indices >= 0; other tiles are left untouched.
- *  x bf16 [m, k], m % 128 == 0; m_indices int32 [m]; out bf16 [m, n]. */
+ * tile whose first row has m_indices >= 0; other tiles are left untouched.  Inside
+ * such a tile the rows after its last row with m_indices >= 0 (the padding the
+ * contract requires to be zeroed) are written as zeros without being computed: what
+ * the reference's kernel produces from their all-zero activations.
+ *  x bf16 [m, k], m % 128 == 0; m_indices int32 [m]; out bf16 [m, n];
+ *  enable_pdl != 0 launches with the programmatic stream-serialization attribute
+ *  (launcher.cpp:440-451). */
 int chord_b200_contiguous(const void* x, const int32_t* packed, const void* scale,
                           const int32_t* m_indices, void* out, int32_t* locks, int64_t num_locks,
                           void* workspace, int64_t workspace_bytes, int32_t* status, int64_t m,
-                          int64_t n, int64_t k, int64_t num_experts, void* stream);
+                          int64_t n, int64_t k, int64_t num_experts, int enable_pdl, void* stream);
 
 /* ---- masked GEMM: replaces launch_grouped_w4a16_masked (launcher.cpp:459-503) --
  * out[g, r, :] = x[g, r, :] . dequant(W[g])^T for r < masked_m[g]; other rows are
  * left untouched.
  *  x bf16 [num_groups, max_m, k]; masked_m int32 [num_groups];
- *  out bf16 [num_groups, max_m, n]; tile_m from chord_b200_masked_tile_m(). */
+ *  out bf16 [num_groups, max_m, n]; tile_m from chord_b200_masked_tile_m();
+ *  enable_pdl as for chord_b200_contiguous. */
 int chord_b200_masked(const void* x, const int32_t* packed, const void* scale,
                       const int32_t* masked_m, void* out, int32_t* locks, int64_t num_locks,
                       void* workspace, int64_t workspace_bytes, int32_t* status,
                       int64_t num_groups, int64_t max_m, int64_t n, int64_t k, int64_t tile_m,
-                      void* stream);
+                      int enable_pdl, void* stream);
 
 /* ---- SiLU * mul between gate_up and down --------------------------------------
  * out[r, j] = silu(in[r, j]) * in[r, inter + j], in bf16 [rows, 2*inter], out bf16
