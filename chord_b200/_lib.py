@@ -35,6 +35,8 @@ SIGNATURES = {
     "chord_b200_schedule_segments": (_i64, [_i64, _i64, _i64, _i64, _ptr, _i64]),
     "chord_b200_indexed": (_int, [_ptr, _ptr, _ptr, _ptr, _i64, _ptr, _i64, _ptr, _ptr, _ptr, _i64,
                                   _ptr, _i64, _ptr, _i64, _i64, _i64, _i64, _i64, _i64, _ptr]),
+    "chord_b200_indexed_rows": (_int, [_ptr, _ptr, _ptr, _ptr, _i64, _ptr, _i64, _ptr, _ptr, _ptr, _i64,
+                                       _ptr, _i64, _ptr, _i64, _i64, _i64, _i64, _i64, _i64, _ptr]),
     "chord_b200_indexed_static_scratch": (_int, [_ptr, _ptr, _ptr, _ptr, _i64, _ptr, _i64, _ptr, _ptr,
                                                  _ptr, _i64, _ptr, _i64, _i64, _i64, _i64, _i64, _i64,
                                                  _ptr]),
@@ -46,6 +48,14 @@ SIGNATURES = {
     "chord_b200_silu_mul_routed": (_int, [_ptr, _ptr, _ptr, _i64, _ptr, _i64, _i64, _ptr]),
     "chord_b200_moe_align_block_size": (_int, [_ptr, _i64, _i64, _i64, _i64, _ptr, _i64, _ptr,
                                                _i64, _ptr, _ptr]),
+    "chord_b200_ep_state_bytes": (_i64, []),
+    "chord_b200_ep_plan": (_int, [_ptr, _i64, _i64, _i64, _i64, _ptr, _ptr, _i64, _ptr]),
+    "chord_b200_ep_dispatch": (_int, [_ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _i64, _i64, _ptr, _ptr,
+                                      _ptr, _ptr, _i64, _i64, _ptr]),
+    "chord_b200_ep_align": (_int, [_ptr, _ptr, _i64, _i64, _i64, _i64, _i64, _ptr, _i64, _ptr, _i64, _ptr,
+                                   _ptr, _ptr, _i64, _i64, _ptr, _i64, _ptr]),
+    "chord_b200_ep_combine_signal": (_int, [_ptr, _i64, _i64, _i64, _ptr]),
+    "chord_b200_ep_combine_wait": (_int, [_ptr, _i64, _i64, _ptr]),
 }
 
 

@@ -18,7 +18,7 @@ from pathlib import Path
 PACKAGE_DIR = Path(__file__).resolve().parent
 CSRC = PACKAGE_DIR / "csrc"
 LIB_PATH = PACKAGE_DIR / "libchord_b200.so"
-SOURCES = ("core.cu", "gemm.cu", "pack.cu", "fused.cu")
+SOURCES = ("core.cu", "gemm.cu", "pack.cu", "fused.cu", "ep.cu")
 ARCH_FLAGS = ("-gencode", "arch=compute_100a,code=sm_100a")
 
 

@@ -255,7 +255,8 @@ int launch_gemm(GemmParams p, const void* x, const int32_t* packed, const void* 
   CHORD_REQUIRE(p.num_experts > 0, "num_experts must be positive");
   CHORD_REQUIRE(p.tile_tokens > 0 && p.tile_tokens <= kMaxTileTokens,
                 "token tile %d must be in [1, %d]", p.tile_tokens, kMaxTileTokens);
-  CHORD_REQUIRE(x != nullptr && packed != nullptr && scale != nullptr && p.out != nullptr,
+  CHORD_REQUIRE(x != nullptr && packed != nullptr && scale != nullptr &&
+                    (p.out != nullptr || p.out_row_ptr != nullptr),
                 "null tensor pointer");
   CHORD_REQUIRE((reinterpret_cast<uintptr_t>(p.out) & 15u) == 0,
                 "the output tensor must be 16-byte aligned");
@@ -503,12 +504,12 @@ int64_t chord_b200_schedule_segments(int64_t tiles, int64_t k, int64_t grid, int
   return count;
 }
 
-int chord_b200_indexed(const void* x, const int32_t* packed, const void* scale,
-                       const int32_t* sorted_ids, int64_t sorted_len, const int32_t* expert_ids,
-                       int64_t expert_len, const int32_t* num_tokens_padded, void* out,
-                       int32_t* locks, int64_t num_locks, void* workspace, int64_t workspace_bytes,
-                       int32_t* status, int64_t m, int64_t n, int64_t k, int64_t num_experts,
-                       int64_t top_k, int64_t block_m, void* stream) {
+static int indexed_launch(const void* x, const int32_t* packed, const void* scale,
+                          const int32_t* sorted_ids, int64_t sorted_len, const int32_t* expert_ids,
+                          int64_t expert_len, const int32_t* num_tokens_padded, void* out,
+                          void* const* out_rows, int32_t* locks, int64_t num_locks, void* workspace,
+                          int64_t workspace_bytes, int32_t* status, int64_t m, int64_t n, int64_t k,
+                          int64_t num_experts, int64_t top_k, int64_t block_m, void* stream) {
   CHORD_REQUIRE(m > 0, "inputs must be non-empty, got m=%lld", static_cast<long long>(m));
   CHORD_REQUIRE(top_k > 0, "top_k must be positive, got %lld", static_cast<long long>(top_k));
   CHORD_REQUIRE(block_m > 0 && block_m % 8 == 0 && block_m <= chord::kMaxTileTokens,
@@ -534,10 +535,35 @@ int chord_b200_indexed(const void* x, const int32_t* packed, const void* scale,
   p.num_tokens_padded = num_tokens_padded;
   p.x = static_cast<const __nv_bfloat16*>(x);
   p.out = static_cast<__nv_bfloat16*>(out);
+  p.out_row_ptr = out_rows;
   p.workspace = static_cast<float*>(workspace);
   p.locks = locks;
   p.status = status;
   return chord::launch_gemm(p, x, packed, scale, num_locks, workspace_bytes, stream);
+}
+
+int chord_b200_indexed(const void* x, const int32_t* packed, const void* scale,
+                       const int32_t* sorted_ids, int64_t sorted_len, const int32_t* expert_ids,
+                       int64_t expert_len, const int32_t* num_tokens_padded, void* out,
+                       int32_t* locks, int64_t num_locks, void* workspace, int64_t workspace_bytes,
+                       int32_t* status, int64_t m, int64_t n, int64_t k, int64_t num_experts,
+                       int64_t top_k, int64_t block_m, void* stream) {
+  CHORD_REQUIRE(out != nullptr, "null output pointer");
+  return indexed_launch(x, packed, scale, sorted_ids, sorted_len, expert_ids, expert_len,
+                        num_tokens_padded, out, nullptr, locks, num_locks, workspace, workspace_bytes,
+                        status, m, n, k, num_experts, top_k, block_m, stream);
+}
+
+int chord_b200_indexed_rows(const void* x, const int32_t* packed, const void* scale,
+                            const int32_t* sorted_ids, int64_t sorted_len, const int32_t* expert_ids,
+                            int64_t expert_len, const int32_t* num_tokens_padded, void* const* out_rows,
+                            int32_t* locks, int64_t num_locks, void* workspace, int64_t workspace_bytes,
+                            int32_t* status, int64_t m, int64_t n, int64_t k, int64_t num_experts,
+                            int64_t top_k, int64_t block_m, void* stream) {
+  CHORD_REQUIRE(out_rows != nullptr, "null row-address table");
+  return indexed_launch(x, packed, scale, sorted_ids, sorted_len, expert_ids, expert_len,
+                        num_tokens_padded, nullptr, out_rows, locks, num_locks, workspace,
+                        workspace_bytes, status, m, n, k, num_experts, top_k, block_m, stream);
 }
 
 int chord_b200_indexed_static_scratch(const void* x, const int32_t* packed, const void* scale,

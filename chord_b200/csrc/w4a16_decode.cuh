@@ -152,7 +152,8 @@ struct StepStream {
 // worker's other three warps; a stream-K slice does (lock, partials), and only then do
 // the four warps meet at named barriers.  Kept out of line: it runs once per tile, and
 // inlined into the dequantisation loop it took registers from that loop.
-static __device__ __noinline__ void decode_drain(uint32_t d_addr, __nv_bfloat16* out_tile, int32_t ldn,
+static __device__ __noinline__ void decode_drain(uint32_t d_addr, __nv_bfloat16* out_tile,
+                                                 void* const* out_rows, int32_t col0, int32_t ldn,
                                           int32_t rows, int32_t mma_n, int32_t seg_type, int32_t seg_peer,
                                           float* workspace, size_t ws_slot, int32_t worker_id,
                                           int32_t* locks, int32_t lock_spins, int32_t* status,
@@ -222,7 +223,13 @@ static __device__ __noinline__ void decode_drain(uint32_t d_addr, __nv_bfloat16*
         const int32_t row = __shfl_sync(0xffffffffu, rows, c0 + 8 * half + static_cast<int32_t>(tj));
         const uint4 val = *reinterpret_cast<const uint4*>(stage + tj * 32 + pc * 8);
         if (row >= 0) {
-          *reinterpret_cast<uint4*>(out_tile + static_cast<size_t>(row) * ldn + pc * 8) = val;
+          if (out_rows != nullptr) {
+            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(
+                __ldg(reinterpret_cast<const unsigned long long*>(out_rows) + row));
+            if (dst != nullptr) *reinterpret_cast<uint4*>(dst + col0 + pc * 8) = val;
+          } else {
+            *reinterpret_cast<uint4*>(out_tile + static_cast<size_t>(row) * ldn + pc * 8) = val;
+          }
         }
         __syncwarp();
       }
@@ -529,7 +536,8 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
     const size_t ws_slot = static_cast<size_t>(kBlockN) * p.mma_n;
 
     auto drain = [&](const Segment& sg, int32_t rows, int32_t n0, uint32_t dcol, int32_t mma_n) {
-      decode_drain(tmem_base + ((q * 32u) << 16) + dcol, p.out + n0 + q * 32, p.n, rows, mma_n, sg.type,
+      decode_drain(tmem_base + ((q * 32u) << 16) + dcol, p.out + n0 + q * 32, p.out_row_ptr,
+                   n0 + static_cast<int32_t>(q) * 32, p.n, rows, mma_n, sg.type,
                    sg.peer, p.workspace, ws_slot, worker_id, p.locks, p.lock_spins, p.status,
                    &ws.stage[q][0][0], bar_id, wt, bad == 0);
     };

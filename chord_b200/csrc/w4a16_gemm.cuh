@@ -135,6 +135,7 @@ struct GemmParams {
   const int32_t* masked_m;
   const __nv_bfloat16* x;
   __nv_bfloat16* out;
+  void* const* out_row_ptr;  // optional (indexed): out_row_ptr[id] = address of the row that receives routed id's result
   float* workspace;     // grid * 128 * mma_n floats
   int32_t* locks;
   int32_t* status;
@@ -1182,7 +1183,14 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
           const int32_t row = sh.out_row[c0 + tj];
           const uint4 v = *reinterpret_cast<const uint4*>(stage + tj * 32 + piece * 8);
           if (row >= 0) {
-            *reinterpret_cast<uint4*>(out_tile + static_cast<size_t>(row) * p.n + piece * 8) = v;
+            if (p.out_row_ptr != nullptr) {
+              // the row lives wherever the caller's table says (possibly on another GPU)
+              __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(
+                  __ldg(reinterpret_cast<const unsigned long long*>(p.out_row_ptr) + row));
+              if (dst != nullptr) *reinterpret_cast<uint4*>(dst + t.n0 + q * 32 + piece * 8) = v;
+            } else {
+              *reinterpret_cast<uint4*>(out_tile + static_cast<size_t>(row) * p.n + piece * 8) = v;
+            }
           }
         }
         __syncwarp();

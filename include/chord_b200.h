@@ -144,6 +144,23 @@ int chord_b200_indexed(const void* x, const int32_t* packed, const void* scale,
                        int32_t* status, int64_t m, int64_t n, int64_t k, int64_t num_experts,
                        int64_t top_k, int64_t block_m, void* stream);
 
+/* ---- indexed GEMM with a table of output row addresses ----------------------------
+ * No counterpart in the reference, whose epilogue stores row `id` at out + id * n
+ * (include/humming/epilogue/gmem_writer.cuh:93-103).  Same operation and arguments as
+ * chord_b200_indexed, except that the result of routed id goes to the BF16 row whose
+ * address is out_rows[id] (a device array of m * top_k addresses, each 16-byte
+ * aligned; a null entry drops the row).  The addresses may lie in another GPU's memory
+ * that is mapped into this process: the expert-parallel layer uses this to let the
+ * down projection store every result row straight into the result tensor of the GPU
+ * the token came from (the combine step of the exchange, done by the epilogue's own
+ * peer stores). */
+int chord_b200_indexed_rows(const void* x, const int32_t* packed, const void* scale,
+                            const int32_t* sorted_ids, int64_t sorted_len, const int32_t* expert_ids,
+                            int64_t expert_len, const int32_t* num_tokens_padded, void* const* out_rows,
+                            int32_t* locks, int64_t num_locks, void* workspace, int64_t workspace_bytes,
+                            int32_t* status, int64_t m, int64_t n, int64_t k, int64_t num_experts,
+                            int64_t top_k, int64_t block_m, void* stream);
+
 /* ---- indexed GEMM without a workspace argument ---------------------------------
  * No counterpart in the reference (its launcher always takes the stream-K scratch
  * from torch's allocator).  Same operation and arguments as chord_b200_indexed, but
@@ -231,6 +248,57 @@ int chord_b200_moe_align_block_size(const int32_t* topk_ids, int64_t numel, int6
                                     int64_t num_experts, int64_t block_m, int32_t* sorted_ids,
                                     int64_t sorted_cap, int32_t* expert_ids, int64_t expert_cap,
                                     int32_t* num_tokens_padded, void* stream);
+
+/* ---- expert-parallel exchange over peer memory -------------------------------------
+ * No counterpart in the reference, which has no communication code ("EP routing may
+ * carry only this rank's routes", docs/getting_started.md:21).  One process per GPU;
+ * experts are split contiguously, rank r owning [r * experts_per_rank, (r + 1) *
+ * experts_per_rank).  The host maps four buffers of every rank into every process
+ * (symmetric memory, CUDA IPC) and passes device arrays of the `world` addresses as this
+ * process sees them:
+ *   peer_state     exchange state of chord_b200_ep_state_bytes() bytes, zeroed once
+ *   peer_recv_x    bf16 [capacity, hidden]: routed activation rows arriving at the owner
+ *   peer_recv_tag  int32 [2, capacity]: local expert of each arriving row, then
+ *                  source rank << 24 | route
+ *   peer_routed    bf16 [routed_rows_per_rank, hidden]: result rows, route order
+ * `epoch` is a counter every rank advances by one per layer call (1, 2, ...): flags
+ * carry it, nothing is reset between calls.  The kernels use plain peer loads and
+ * stores, no TMA and no multicast.  Every cross-GPU wait is bounded (about five
+ * seconds); a wait that runs out ORs a bit into the `status` word at the end of the
+ * state (256 counts, 512 rows, 1024 results, 2048 receive buffer too small) and the
+ * kernel carries on with incomplete data instead of hanging.
+ * One layer call, all on one stream:
+ *   chord_b200_ep_plan      send_pos[i] = position of route i among this rank's routes to
+ *                           the same destination (-1 for an expert outside all ranks);
+ *                           publishes the per-destination counts to every peer
+ *   chord_b200_ep_dispatch  waits for all counts, copies every route's row and tag into
+ *                           its owner's receive buffers (rows ordered by source rank,
+ *                           then route), flags every peer
+ *   chord_b200_ep_align     on the owner: waits for all rows; recv_count = rows received;
+ *                           sorted_ids / expert_ids / num_tokens_padded over the received
+ *                           expert tags as chord_b200_moe_align_block_size produces them
+ *                           (sentinel = capacity); row_ptr[i] = address in the source
+ *                           rank's peer_routed of the row that receives row i's result
+ *   (gate_up = chord_b200_indexed on recv_x with m = capacity, top_k = 1; SiLU*mul;
+ *    down = chord_b200_indexed_rows with out_rows = row_ptr)
+ *   chord_b200_ep_combine_signal   flags every peer: this owner's results are stored
+ *   chord_b200_ep_combine_wait     returns (stream-ordered) once every owner has flagged */
+int64_t chord_b200_ep_state_bytes(void);
+int chord_b200_ep_plan(const int32_t* topk_ids, int64_t routes, int64_t experts_per_rank, int64_t world,
+                       int64_t rank, int32_t* send_pos, void* const* peer_state, int64_t epoch,
+                       void* stream);
+int chord_b200_ep_dispatch(const void* x, const int32_t* topk_ids, const int32_t* send_pos, int64_t routes,
+                           int64_t top_k, int64_t hidden, int64_t experts_per_rank, int64_t world,
+                           int64_t rank, void* state, void* const* peer_state, void* const* peer_recv_x,
+                           void* const* peer_recv_tag, int64_t capacity, int64_t epoch, void* stream);
+int chord_b200_ep_align(void* state, const int32_t* recv_tag, int64_t capacity, int64_t world, int64_t rank,
+                        int64_t num_local_experts, int64_t block_m, int32_t* sorted_ids, int64_t sorted_cap,
+                        int32_t* expert_ids, int64_t expert_cap, int32_t* num_tokens_padded,
+                        int32_t* recv_count, void* const* peer_routed, int64_t routed_rows_per_rank,
+                        int64_t hidden, void** row_ptr, int64_t epoch, void* stream);
+int chord_b200_ep_combine_signal(void* const* peer_state, int64_t world, int64_t rank, int64_t epoch,
+                                 void* stream);
+int chord_b200_ep_combine_wait(void* state, int64_t world, int64_t epoch, void* stream);
 
 #ifdef __cplusplus
 }

@@ -17,6 +17,9 @@ reference's own ``pack_w4a16`` produced on a B200
 (``tests/golden/reference_gpu.npz``, made by
 ``tests/golden/make_reference_gpu_golden.py``); ``reference_indexed`` is checked
 against the BF16 output of the reference's ``indexed`` kernel from the same run.
+``reference_masked`` / ``reference_contiguous`` are checked against the inputs and
+expected outputs the reference's own grouped tests build on the CPU
+(``make_masked_case`` / ``make_contiguous_case``, ``tests/golden/grouped.npz``).
 """
 
 from __future__ import annotations
@@ -268,14 +271,27 @@ def reference_indexed_rowwise(activation, codes, scale, topk_ids, top_k, project
     return out
 
 
+def _dequantize_f32(codes: torch.Tensor, scale: torch.Tensor, dequant: str) -> torch.Tensor:
+    """FP32 weights of one expert: ``"bf16"`` rounds ``(code - 8) * scale`` to BF16 first
+    (what the kernels compute), ``"fp32"`` does not (what the reference's grouped tests
+    compare against, tests/test_w4a16_grouped.py:74-82)."""
+    if dequant == "bf16":
+        return dequantize_bf16(codes, scale).float()
+    if dequant == "fp32":
+        return dequant_reference_fp32(codes, scale)
+    raise ValueError(f"dequant must be 'bf16' or 'fp32', got {dequant!r}")
+
+
 def reference_contiguous(x2: torch.Tensor, codes: torch.Tensor, scale: torch.Tensor,
-                         m_indices: torch.Tensor, block: int = 128) -> torch.Tensor:
+                         m_indices: torch.Tensor, block: int = 128, dequant: str = "bf16") -> torch.Tensor:
     """FP32 ``D[r] = x2[r] . deq(W[m_indices[tile first row]])^T`` per 128-row tile;
-    tiles whose first row has index < 0 stay NaN (not written).
+    tiles whose first row has index < 0 stay NaN (not written).  Padding rows inside a
+    computed tile come out as the product of their (zeroed) activations, i.e. zeros.
 
     Follows the contiguous scheduler (include/deep_gemm/scheduler/gemm.cuh:273-274,
     include/deep_gemm/impls/sm90_w4a16_gemm.cuh:237-238) with the BF16
-    dequantisation the kernels use (include/deep_gemm/ptx/ld_st.cuh:15-40).
+    dequantisation the kernels use (include/deep_gemm/ptx/ld_st.cuh:15-40), and the
+    per-expert reference of tests/test_w4a16_grouped.py:225-241 (``dequant="fp32"``).
     """
     m = x2.size(0)
     out = torch.full((m, codes.size(1)), float("nan"), dtype=torch.float32)
@@ -285,18 +301,18 @@ def reference_contiguous(x2: torch.Tensor, codes: torch.Tensor, scale: torch.Ten
         if e < 0:
             continue
         if e not in cache:
-            cache[e] = dequantize_bf16(codes[e], scale[e]).float()
+            cache[e] = _dequantize_f32(codes[e], scale[e], dequant)
         out[start:start + block] = x2[start:start + block].float() @ cache[e].t()
     return out
 
 
 def reference_masked(x3: torch.Tensor, codes: torch.Tensor, scale: torch.Tensor,
-                     masked_m: torch.Tensor) -> torch.Tensor:
+                     masked_m: torch.Tensor, dequant: str = "bf16") -> torch.Tensor:
     """FP32 ``D[g, :masked_m[g]] = x3[g, :masked_m[g]] . deq(W[g])^T``; other rows NaN.
 
     Follows chord_kernels/operator/grouped/api.py:116-133 (contract) and
-    tests/test_w4a16_grouped.py:190-196 (per-group reference), with BF16
-    dequantisation as in the kernels.
+    tests/test_w4a16_grouped.py:190-196 (per-group reference, ``dequant="fp32"``); the
+    default is the BF16 dequantisation the kernels use.
     """
     g_count, max_m, _ = x3.shape
     out = torch.full((g_count, max_m, codes.size(1)), float("nan"), dtype=torch.float32)
@@ -304,7 +320,7 @@ def reference_masked(x3: torch.Tensor, codes: torch.Tensor, scale: torch.Tensor,
         mm = min(int(masked_m[g]), max_m)
         if mm <= 0:
             continue
-        w = dequantize_bf16(codes[g], scale[g]).float()
+        w = _dequantize_f32(codes[g], scale[g], dequant)
         out[g, :mm] = x3[g, :mm].float() @ w.t()
     return out
 

@@ -6,6 +6,9 @@ uniform in [0.005, 0.02]; routing as tests/generators.py:140-230 of the referenc
 
 from __future__ import annotations
 
+from pathlib import Path
+
+import numpy as np
 import torch
 
 from oracle import w4a16_oracle as O
@@ -64,3 +67,26 @@ def make_contiguous_case(counts, n, k, seed, extra_padding_tiles=0):
     x2 = torch.randn((len(idx), k), generator=g).to(torch.bfloat16)
     x2[m_indices < 0] = 0
     return dict(codes=codes, scale=scale, x2=x2, m_indices=m_indices)
+
+
+def load_grouped_golden(name):
+    """One case of tests/golden/grouped.npz: inputs and expected BF16 outputs built by the
+    reference's own ``make_masked_case`` / ``make_contiguous_case`` on the CPU."""
+    z = np.load(Path(__file__).resolve().parent / "golden" / "grouped.npz")
+
+    def bf16(key):
+        return torch.from_numpy(z[f"{name}_{key}"].copy()).view(torch.bfloat16)
+
+    shape = [int(v) for v in z[f"{name}_shape"]]
+    n, k = shape[-2], shape[-1]
+    groups = shape[0]
+    codes = torch.from_numpy(O.unpack_checkpoint_uint4(z[f"{name}_checkpoint"])).reshape(groups, n, k)
+    case = dict(codes=codes, scale=bf16("scale"), x=bf16("x"), ref=bf16("ref"), n=n, k=k, groups=groups,
+                cosine_limit=float(z["cosine_limit"]))
+    if name.startswith("masked"):
+        case.update(max_m=shape[1], expected_m=shape[2],
+                    masked_m=torch.from_numpy(z[f"{name}_masked_m"].copy()))
+    else:
+        case.update(m_indices=torch.from_numpy(z[f"{name}_m_indices"].copy()),
+                    bounds=[tuple(int(v) for v in b) for b in z[f"{name}_bounds"]])
+    return case

@@ -1,15 +1,16 @@
 """Generates tests/golden/*.npz by running the reference's own CPU-runnable code.
 
-Run once in a container that has the reference checkout (read-only) at
-``/root/reference``:
+Run once in a container that has a read-only checkout of the reference:
 
-    python tests/golden/make_golden.py
+    CHORD_REFERENCE=<path to the checkout> python tests/golden/make_golden.py
 
 What it runs, unmodified, from the reference:
   * tests/generators.py: ``generate_topk_ids``, ``align_routing_blocks``,
     ``reference_indexed``, ``pack_checkpoint_uint4``
   * chord_kernels/operator/packing.py: ``_pack_weight_scale``
-  * tests/test_w4a16_grouped.py: ``_dequant_reference``
+  * tests/test_w4a16_grouped.py: ``_dequant_reference``, and for ``grouped.npz``
+    ``make_masked_case`` / ``make_contiguous_case`` on ``device="cpu"``: the inputs
+    and the expected outputs of the reference's own masked and contiguous tests
   * tests/roofline.py: ``traffic_bytes``, ``error_metrics``
 The reference's packer itself (``repack_w4a16``) is a CUDA kernel and cannot run
 without a GPU, so the packed-weight layout has no golden vector here.
@@ -29,17 +30,62 @@ from pathlib import Path
 import numpy as np
 import torch
 
-REFERENCE = Path(os.environ.get("CHORD_REFERENCE", "/root/reference"))
 OUT = Path(__file__).resolve().parent
+
+
+def reference_root() -> Path:
+    root = os.environ.get("CHORD_REFERENCE") or (sys.argv[1] if len(sys.argv) > 1 else None)
+    if not root or not (Path(root) / "chord_kernels").is_dir():
+        raise SystemExit("set CHORD_REFERENCE (or pass the path) to a checkout of the reference")
+    return Path(root)
 
 
 def bf16_bits(t: torch.Tensor) -> np.ndarray:
     return t.contiguous().view(torch.int16).numpy().copy()
 
 
+def grouped_cases(gen) -> None:
+    """Inputs and expected outputs of the reference's masked / contiguous tests
+    (tests/test_w4a16_grouped.py:168-242), small shapes, CPU.  Masked: groups whose
+    valid-row count reaches max_m next to partial ones, and a second case with a few
+    rows per group.  Contiguous: experts shorter than their 128-row run (trailing -1
+    rows, zeroed activations) and a case with two full blocks per expert."""
+    import test_w4a16_grouped as grouped  # reference tests/test_w4a16_grouped.py
+
+    cpu = torch.device("cpu")
+    arrays = {}
+    masked = {"masked_a": grouped.MaskedCase(4, 32, 30, 128, 256),
+              "masked_b": grouped.MaskedCase(3, 64, 8, 256, 128)}
+    for name, case in masked.items():
+        a3, codes, scale, masked_m, ref = grouped.make_masked_case(case, cpu)
+        arrays[f"{name}_shape"] = np.array([case.num_groups, case.max_m, case.expected_m_per_group,
+                                            case.n, case.k], dtype=np.int64)
+        arrays[f"{name}_x"] = bf16_bits(a3)
+        arrays[f"{name}_checkpoint"] = gen.pack_checkpoint_uint4(codes).numpy()
+        arrays[f"{name}_scale"] = bf16_bits(scale)
+        arrays[f"{name}_masked_m"] = masked_m.numpy()
+        arrays[f"{name}_ref"] = bf16_bits(ref)
+    contiguous = {"contiguous_a": grouped.ContiguousCase(3, 100, 128, 256),
+                  "contiguous_b": grouped.ContiguousCase(2, 256, 256, 128)}
+    for name, case in contiguous.items():
+        a2, codes, scale, m_indices, ref, bounds = grouped.make_contiguous_case(case, cpu)
+        arrays[f"{name}_shape"] = np.array([case.num_groups, case.expected_m_per_group, case.n,
+                                            case.k], dtype=np.int64)
+        arrays[f"{name}_x"] = bf16_bits(a2)
+        arrays[f"{name}_checkpoint"] = gen.pack_checkpoint_uint4(codes).numpy()
+        arrays[f"{name}_scale"] = bf16_bits(scale)
+        arrays[f"{name}_m_indices"] = m_indices.numpy()
+        arrays[f"{name}_ref"] = bf16_bits(ref)
+        arrays[f"{name}_bounds"] = np.array(bounds, dtype=np.int64)
+    arrays["cosine_limit"] = np.array(grouped._COSINE_LIMIT)
+    np.savez_compressed(OUT / "grouped.npz", **arrays)
+    print("grouped written", (OUT / "grouped.npz").stat().st_size, "bytes")
+
+
 def main() -> None:
-    sys.path.insert(0, str(REFERENCE / "tests"))
-    sys.path.insert(0, str(REFERENCE))
+    reference = reference_root()
+    sys.path.insert(0, str(reference / "tests"))
+    sys.path.insert(0, str(reference))
     os.environ.setdefault("CHORD_CACHE_DIR", "/tmp/chord_cache")
     os.environ.setdefault("CHORD_TMP_DIR", "/tmp/chord_tmp")
     import generators as gen  # reference tests/generators.py
@@ -82,6 +128,7 @@ def main() -> None:
             cos_self=np.array(roofline.error_metrics(ref_gate_up, ref_gate_up)[0]),
         )
         print(name, "written", (OUT / f"{name}.npz").stat().st_size, "bytes")
+    grouped_cases(gen)
 
 
 if __name__ == "__main__":

@@ -140,3 +140,39 @@ def test_schedule_rejects_bad_queries(native_lib):
     assert native_lib.chord_b200_schedule_segments(10, 100, 148, 0, None, 0) < 0
     assert native_lib.chord_b200_schedule_segments(10, 128, 148, 148, None, 0) < 0
     assert native_lib.chord_b200_schedule_segments(10, 128, 148, 3, None, 0) >= 0
+
+
+def test_misaligned_pointers_are_refused_before_any_launch(native_lib):
+    """The kernels read activations and the SiLU*mul operands in 16-byte pieces: a pointer
+    that is not 16-byte aligned comes back as return code 1 from the argument checks (no
+    device is touched, so this runs without a GPU)."""
+    from chord_b200 import _lib
+
+    ok, odd = 0x7F0000000000, 0x7F0000000008
+    lib = native_lib
+    assert lib.chord_b200_silu_mul(odd, ok, 4, 64, None) == 1
+    assert "aligned" in _lib.last_error()
+    assert lib.chord_b200_silu_mul(ok, odd, 4, 64, None) == 1
+    assert lib.chord_b200_silu_mul_routed(odd, ok, ok, 16, ok, 4, 64, None) == 1
+
+    def indexed(x, workspace, out):
+        return lib.chord_b200_indexed(x, ok, ok, ok, 16, ok, 1, ok, out, ok, 1024, workspace, 1 << 20,
+                                      None, 4, 128, 64, 1, 1, 16, None)
+
+    assert indexed(odd, ok, ok) == 1 and "activation" in _lib.last_error()
+    assert indexed(ok, odd, ok) == 1 and "workspace" in _lib.last_error()
+    assert indexed(ok, ok, odd) == 1 and "output" in _lib.last_error()
+    assert lib.chord_b200_masked(odd, ok, ok, ok, ok, ok, 1024, ok, 1 << 20, None, 2, 16, 128, 64, 16,
+                                 0, None) == 1
+    assert lib.chord_b200_contiguous(odd, ok, ok, ok, ok, ok, 1024, ok, 1 << 20, None, 128, 128, 64, 2,
+                                     0, None) == 1
+
+
+def test_option_names_are_all_documented(native_lib):
+    """Every option chord_b200_set_option accepts is listed in the header's comment."""
+    header = (ROOT / "include" / "chord_b200.h").read_text()
+    source = (ROOT / "chord_b200" / "csrc" / "core.cu").read_text()
+    names = re.findall(r'std::strcmp\(name, "(\w+)"\)', source)
+    assert len(names) >= 12
+    for name in names:
+        assert f'"{name}"' in header, f"option {name} is missing from include/chord_b200.h"

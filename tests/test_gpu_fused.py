@@ -79,3 +79,52 @@ def test_single_gpu_layer_matches_oracle(device):
     got = out.float().cpu().view(tokens * top_k, hidden)
     assert O.cosine_diff(got, ref) <= 5e-3
     assert O.max_abs_rel(got, ref) <= 2e-2      # two GEMMs and an activation in BF16
+
+
+@pytest.mark.parametrize("world,tokens,top_k", [(2, 24, 2), (4, 33, 4)])
+def test_peer_memory_exchange_with_all_ranks_on_one_gpu(device, world, tokens, top_k):
+    """The expert-parallel layer's own kernels (plan, dispatch by peer stores, receive-side
+    alignment, down projection storing into the source rank's result tensor, flags) with
+    every rank living on this one GPU: each step is run for all ranks before the next, so
+    no kernel waits for a later launch.  Every rank's routed outputs must equal the
+    oracle's gate_up -> SiLU*mul -> down on the owning expert's weights."""
+    import chord_b200
+    from chord_b200 import ep
+
+    experts_total, hidden, inter = 8, 256, 128
+    per_rank = experts_total // world
+    codes13, scale13 = make_weights(experts_total, 2 * inter, hidden, seed=61)
+    codes2, scale2 = make_weights(experts_total, hidden, inter, seed=62)
+    lib_state = chord_b200._lib.load().chord_b200_ep_state_bytes()
+    layout = ep.ExchangeLayout.build(world, tokens, top_k, hidden, hidden, lib_state)
+    fabric = ep.LocalFabric(layout.total, world, device)
+    layers, xs, topks = [], [], []
+    g = torch.Generator().manual_seed(63)
+    for r in range(world):
+        lo, hi = r * per_rank, (r + 1) * per_rank
+        w13 = chord_b200.pack_w4a16(codes13[lo:hi].to(device), scale13[lo:hi].to(device))
+        w2 = chord_b200.pack_w4a16(codes2[lo:hi].to(device), scale2[lo:hi].to(device))
+        layers.append(ep.ExpertParallelLayer(w13, w2, num_experts_total=experts_total, max_tokens=tokens,
+                                             top_k=top_k, fabric=fabric.view(r)))
+        n_tok = tokens - r                       # ranks bring different token counts
+        xs.append(torch.randn((n_tok, hidden), generator=g).to(torch.bfloat16))
+        topks.append(O.topk_ids_random(n_tok, top_k, experts_total, g))
+    for call in range(2):                        # two calls: epochs advance, nothing is reset
+        for r, layer in enumerate(layers):
+            layer.plan(xs[r].to(device), topks[r].to(device))
+        for layer in layers:
+            layer.dispatch()
+        for layer in layers:
+            layer.local_experts()
+        outs = [layer.finish().float().cpu() for layer in layers]
+        for r, layer in enumerate(layers):
+            assert layer.status() == 0
+            n_tok = xs[r].size(0)
+            gate_up = O.reference_indexed(xs[r], codes13, scale13, topks[r], top_k)
+            hidden_rows = O.silu_mul(gate_up.to(torch.bfloat16))
+            ref = O.reference_indexed(hidden_rows, codes2, scale2, topks[r], top_k, projection="down")
+            got = outs[r].reshape(n_tok * top_k, hidden)
+            assert not bool(torch.isnan(got).any())
+            assert O.cosine_diff(got, ref) <= 5e-3
+            assert O.max_abs_rel(got, ref) <= 2e-2   # two GEMMs and an activation, each rounded to BF16
+        xs = [x * 0.5 for x in xs]               # new inputs for the second call

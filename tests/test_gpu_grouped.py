@@ -6,7 +6,8 @@ import pytest
 import torch
 
 from oracle import w4a16_oracle as O
-from tests.cases import make_contiguous_case, make_indexed_case, make_masked_case
+from tests.cases import (load_grouped_golden, make_contiguous_case, make_indexed_case,
+                         make_masked_case)
 
 pytestmark = pytest.mark.gpu
 
@@ -170,3 +171,45 @@ def test_grouped_kernel_variants(device, option, value):
             _compare(mout, ref.reshape(6 * 200, 256))
     finally:
         _lib.set_option(option, defaults[option])
+
+
+@pytest.mark.parametrize("name", ["masked_a", "masked_b"])
+def test_masked_matches_the_references_own_test_vectors(device, name):
+    """Inputs and expected outputs built by the reference's make_masked_case on the CPU
+    (tests/golden/grouped.npz): rows below masked_m within its limit (cos-diff < 1e-3
+    against its FP32-dequantised expectation), rows at or above masked_m untouched."""
+    import chord_b200
+
+    c = load_grouped_golden(name)
+    w = chord_b200.pack_w4a16(c["codes"].to(device), c["scale"].to(device))
+    out = torch.full((c["groups"] * c["max_m"], c["n"]), float("nan"), dtype=torch.bfloat16, device=device)
+    chord_b200.masked(c["x"].to(device), w, c["masked_m"].to(device), c["expected_m"], outputs=out)
+    _status_ok(device)
+    got = out.float().cpu().view(c["groups"], c["max_m"], c["n"])
+    ref = c["ref"].float()
+    for g in range(c["groups"]):
+        mm = int(c["masked_m"][g])
+        assert not bool(torch.isnan(got[g, :mm]).any())
+        assert bool(torch.isnan(got[g, mm:]).all())
+        assert O.cosine_diff(got[g, :mm], ref[g, :mm]) < c["cosine_limit"]
+        assert O.max_abs_rel(got[g, :mm], ref[g, :mm]) <= REL_LIMIT
+
+
+@pytest.mark.parametrize("name", ["contiguous_a", "contiguous_b"])
+def test_contiguous_matches_the_references_own_test_vectors(device, name):
+    """Same for make_contiguous_case: every row of the output equals the reference's
+    expectation, which is zero on the padding rows (index -1) of an expert's run."""
+    import chord_b200
+
+    c = load_grouped_golden(name)
+    w = chord_b200.pack_w4a16(c["codes"].to(device), c["scale"].to(device))
+    m = c["x"].size(0)
+    out = torch.full((m, c["n"]), float("nan"), dtype=torch.bfloat16, device=device)
+    chord_b200.contiguous(c["x"].to(device), w, c["m_indices"].to(device), outputs=out)
+    _status_ok(device)
+    got, ref = out.float().cpu(), c["ref"].float()
+    assert not bool(torch.isnan(got).any())
+    pad = c["m_indices"] < 0
+    assert bool((got[pad] == ref[pad]).all())
+    assert O.cosine_diff(got[~pad], ref[~pad]) < c["cosine_limit"]
+    assert O.max_abs_rel(got[~pad], ref[~pad]) <= REL_LIMIT

@@ -198,7 +198,7 @@ def test_repeatable_with_every_group_count(device, groups, decode_kernel):
 def test_stream_k_split_matches_whole_tiles(device, decode_kernel):
     """Few tiles on many CTAs forces every tile through the stream-K reduction; a
     one-CTA grid computes whole tiles.  FP32 partials summed once: nearly all outputs
-    are bit-equal (the reference asks for >= 99.5 %, tests/test_w4a16_indexed.py:1284)."""
+    are bit-equal; the bound is the reference's 99.5 % (tests/test_w4a16_indexed.py:1284-1285)."""
     from chord_b200 import _lib
 
     case = make_indexed_case(num_experts=2, n=256, k=7168, m=6, top_k=1, block_m=16, seed=22)
@@ -214,7 +214,8 @@ def test_stream_k_split_matches_whole_tiles(device, decode_kernel):
     check_against_oracle(whole, case)
     a, b = split.float().cpu(), whole.float().cpu()
     rows = ~torch.isnan(a).any(dim=1)
-    assert (a[rows] == b[rows]).float().mean() >= 0.9
+    same = float((a[rows] == b[rows]).float().mean())
+    assert same >= 0.995, f"only {same:.4f} of the outputs are bit-equal"
     assert O.max_abs_rel(a[rows], b[rows]) < 1e-2
 
 
@@ -339,3 +340,33 @@ def test_decode_step_replays_from_a_cuda_graph(device):
         assert torch.equal(replayed.view(torch.int16), out.view(torch.int16))
     assert int(status_word(device).item()) == 0
     assert bool((locks == 0).all())
+
+
+def test_lock_wait_gives_up_and_reports(device):
+    """The bounded wait of a stream-K owner, made to run out without hanging anything: the
+    lock words start at a large negative value, so the contributors' increments never
+    reach the count the owner waits for.  With the poll limit set low the launch returns
+    at once, the status word carries the lock-timeout bit, check_status() raises, and a
+    following launch on zeroed locks is correct again."""
+    import chord_b200
+    from chord_b200 import _lib
+    from chord_b200.indexed_gemm import status_word
+
+    case = make_indexed_case(num_experts=2, n=256, k=7168, m=6, top_k=1, block_m=16, seed=22)
+    weight = chord_b200.pack_w4a16(case["codes"].to(device), case["scale"].to(device))
+    args = (case["x"].to(device), weight, case["sorted_ids"].to(device), case["expert_ids"].to(device),
+            case["num_tokens_padded"].to(device).reshape(1), 1)
+    poisoned = torch.full((1024,), -(1 << 20), dtype=torch.int32, device=device)
+    out = torch.zeros((6, 256), dtype=torch.bfloat16, device=device)
+    _lib.set_option("lock_spins", 64)
+    try:
+        chord_b200.indexed(*args, locks=poisoned, outputs=out, block_m=16)
+        torch.cuda.synchronize()
+    finally:
+        _lib.set_option("lock_spins", 1 << 22)
+    assert int(status_word(device).item()) & 16, "the owner's lock wait should have run out"
+    with pytest.raises(RuntimeError, match="lock"):
+        chord_b200.check_status(device)
+    assert int(status_word(device).item()) == 0      # check_status clears the word
+    good, _ = run_case(device, case)                  # fresh locks: correct again
+    check_against_oracle(good, case)

@@ -176,3 +176,51 @@ def test_oracle_indexed_matches_reference_gpu_kernel():
     assert got.shape == ref.shape == (m * top_k, n)
     assert O.cosine_diff(got, ref) <= 5e-3
     assert O.max_abs_rel(got, ref) <= 1e-2
+
+
+# ------------------------------------------------- masked / contiguous goldens --
+
+from tests.cases import load_grouped_golden  # noqa: E402
+
+
+@pytest.mark.parametrize("name", ["masked_a", "masked_b"])
+def test_masked_reference_matches_the_references_own_test_vectors(name):
+    """`reference_masked` against tests/test_w4a16_grouped.py::make_masked_case run on the
+    CPU: the same rows are written (the reference leaves the others zero), the FP32-dequant
+    form reproduces its BF16 values to one rounding, and the BF16-dequant form the kernels
+    implement stays inside the reference's own limit (cos-diff < 1e-3)."""
+    c = load_grouped_golden(name)
+    ref = c["ref"].float()
+    loose = O.reference_masked(c["x"], c["codes"], c["scale"], c["masked_m"], dequant="fp32")
+    exact = O.reference_masked(c["x"], c["codes"], c["scale"], c["masked_m"])
+    written = ~torch.isnan(exact).any(dim=2)
+    for g in range(c["groups"]):
+        mm = int(c["masked_m"][g])
+        assert bool(written[g, :mm].all()) and not bool(written[g, mm:].any())
+        assert bool((ref[g, mm:] == 0).all())
+    assert torch.equal(torch.isnan(loose), torch.isnan(exact))
+    got = loose[written].to(torch.bfloat16).float()
+    # same products, different summation order: at most one BF16 step apart
+    assert bool(((got - ref[written]).abs() <= ref[written].abs() * 2 ** -7 + 1e-6).all())
+    assert O.cosine_diff(exact[written], ref[written]) < c["cosine_limit"]
+    assert O.max_abs_rel(exact[written], ref[written]) <= 1e-2
+
+
+@pytest.mark.parametrize("name", ["contiguous_a", "contiguous_b"])
+def test_contiguous_reference_matches_the_references_own_test_vectors(name):
+    """`reference_contiguous` against make_contiguous_case: every 128-row tile of an expert
+    is written, its rows up to the expert's count carry x . W^T, its padding rows (index
+    -1, zeroed activations) come out as zeros - what the reference expects there."""
+    c = load_grouped_golden(name)
+    ref = c["ref"].float()
+    loose = O.reference_contiguous(c["x"], c["codes"], c["scale"], c["m_indices"], dequant="fp32")
+    exact = O.reference_contiguous(c["x"], c["codes"], c["scale"], c["m_indices"])
+    assert not bool(torch.isnan(exact).any())  # every tile of these cases starts with a valid row
+    pad = c["m_indices"] < 0
+    assert bool((exact[pad] == 0).all()) and bool((ref[pad] == 0).all())
+    for expert, start, end in c["bounds"]:
+        assert bool((c["m_indices"][start:end] == expert).all())
+    got = loose.to(torch.bfloat16).float()
+    assert bool(((got - ref).abs() <= ref.abs() * 2 ** -7 + 1e-6).all())
+    assert O.cosine_diff(exact[~pad], ref[~pad]) < c["cosine_limit"]
+    assert O.max_abs_rel(exact[~pad], ref[~pad]) <= 1e-2
