@@ -2,7 +2,7 @@
 novitalabs/chord; not needed to run the tests, which read the committed .npz).
 
     python tests/golden/make_reference_gpu_golden.py --reference /path/to/chord \
-        [--out tests/golden/reference_gpu.npz] [--time]
+        [--out tests/golden/reference_gpu.npz]
 
 What it records, for seeded inputs generated here:
   * `pack_w4a16` of the reference (its repack kernel, NVRTC-compiled from
@@ -11,9 +11,6 @@ What it records, for seeded inputs generated here:
     the reference's own output.
   * `indexed` of the reference (its Blackwell `mma.sync` schedule) on a small routed
     case: the BF16 output, with the routing it was given.
-With --time it also prints CUDA-event timings of the reference's `indexed` on the
-Kimi-K2.5 EP8 decode shapes (48 local experts of 384), for a same-box comparison.
-
 Nothing of the reference is copied: the script imports it from the path given.
 """
 
@@ -46,9 +43,8 @@ def checkpoint_words(codes: torch.Tensor) -> torch.Tensor:
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="path to a checkout of the reference")
     ap.add_argument("--out", default=str(Path(__file__).resolve().parent / "reference_gpu.npz"))
-    ap.add_argument("--time", action="store_true")
     args = ap.parse_args()
 
     scratch = tempfile.mkdtemp(prefix="chord_ref_")
@@ -107,52 +103,6 @@ def main() -> None:
     print(f"wrote {args.out}: block_m {block_m}, packed {tuple(from_words.packed.shape)}, "
           f"indexed out {tuple(result.shape)}")
 
-    if args.time:
-        time_reference_decode(ref, O, dev)
-
-
-def time_reference_decode(ref, O, dev) -> None:
-    """CUDA-event timings of the reference's `indexed` on the K2.5 EP8 decode shapes."""
-    experts, total, top_k = 48, 384, 8
-    flush = torch.empty(256 * 1024 * 1024, dtype=torch.int8, device=dev)
-    g = torch.Generator().manual_seed(1)
-    weights = {}
-    for name, (n, k) in (("gate_up", (4096, 7168)), ("down", (7168, 2048))):
-        words = torch.randint(-2**31, 2**31 - 1, (experts, n, k // 8), dtype=torch.int64,
-                              generator=g).to(torch.int32)
-        scale = (torch.rand((experts, n, k // 32), generator=g) * 0.015 + 0.005).to(torch.bfloat16)
-        weights[name] = (ref.pack_w4a16(words.to(dev), scale.to(dev), packed=True), n, k)
-    for batch in (16, 64, 256):
-        g = torch.Generator().manual_seed(batch)
-        topk = O.topk_ids_random(batch, top_k, total, g)
-        for name, (w, n, k) in weights.items():
-            block_m = int(ref.indexed_block_m(w, batch, top_k))
-            sorted_ids, expert_ids, padded = O.align_routing_blocks(topk, block_m, experts, 0)
-            active = int(torch.unique(expert_ids).numel())
-            routed = int((sorted_ids < batch * top_k).sum())
-            rows = batch if name == "gate_up" else batch * top_k
-            x = torch.randn((rows, k), generator=g).to(torch.bfloat16).to(dev)
-            outp = torch.empty((batch * top_k, n), dtype=torch.bfloat16, device=dev)
-            locks = torch.zeros(1024, dtype=torch.int32, device=dev)
-            sd, ed, nd = sorted_ids.to(dev), expert_ids.to(dev), padded.to(dev).reshape(1)
-            tk = top_k if name == "gate_up" else 1
-            call = lambda: ref.indexed(x, w, sd, ed, nd, tk, locks=locks, outputs=outp, block_m=block_m)  # noqa: E731
-            for _ in range(3):
-                call()
-            torch.cuda.synchronize()
-            times = []
-            for _ in range(10):
-                flush.zero_()
-                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                a.record()
-                call()
-                b.record()
-                torch.cuda.synchronize()
-                times.append(a.elapsed_time(b) * 1e3)
-            us = float(np.median(times))
-            nbytes = O.traffic_bytes(active, n, k, rows, routed)
-            print(f"reference indexed b{batch} {name}: block_m {block_m} active {active} routed {routed}: "
-                  f"{us:.1f} us  {nbytes / us / 1e3:.0f} GB/s", flush=True)
 
 
 if __name__ == "__main__":
