@@ -549,7 +549,6 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
       const int32_t n_full = seg.ke - seg.kb - (tail ? 1 : 0);
       // Output row of token slot `lane`: loaded now, used in the epilogue.
       const int32_t my_out_row = out_row_of(p, t, static_cast<int32_t>(lane));
-      uint32_t last_bar = afree0, last_ph = slot_ph ^ 1u;
       // One 64-wide step (K half `h` of the stage at `st`), straight-line: the waits
       // record a failure in `bad` and the code runs on (on stale data, within this
       // worker's own shared and tensor memory); `bad` is tested once per stage.
@@ -580,20 +579,14 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
           unbias_word(words[i].y, hi + 4 * i);
         }
         // scales[g].x = {slab A row r, slab A row r+8} of K32 group g; .y = same for slab B.
-        const uint32_t a0_lo = __byte_perm(scales[0].x, 0, 0x1010), a0_hi = __byte_perm(scales[0].x, 0, 0x3232);
-        const uint32_t a1_lo = __byte_perm(scales[1].x, 0, 0x1010), a1_hi = __byte_perm(scales[1].x, 0, 0x3232);
-        const uint32_t b0_lo = __byte_perm(scales[0].y, 0, 0x1010), b0_hi = __byte_perm(scales[0].y, 0, 0x3232);
-        const uint32_t b1_lo = __byte_perm(scales[1].y, 0, 0x1010), b1_hi = __byte_perm(scales[1].y, 0, 0x3232);
         ptx::tc_fence_after();
         const uint32_t a_addr = a_lane + slot_bar * 4u;  // 32 columns per slot
-        ptx::tmem_st_16x128b_x8_scaled(a_addr, lo, a0_lo, a0_hi, a1_lo, a1_hi);
-        ptx::tmem_st_16x128b_x8_scaled(a_addr + (16u << 16), hi, b0_lo, b0_hi, b1_lo, b1_hi);
+        ptx::tmem_st_16x128b_x8_scaled(a_addr, lo, scales[0].x, scales[1].x);
+        ptx::tmem_st_16x128b_x8_scaled(a_addr + (16u << 16), hi, scales[0].y, scales[1].y);
         ptx::tmem_wait_st();
         ptx::tc_fence_before();
-        __syncwarp();
+        // (the wait above is warp-wide: every lane's stores are complete when lane 0 arrives)
         ptx::mbar_arrive_lane0(afull0 + slot_bar, lane);
-        last_bar = afree;
-        last_ph = slot_ph;
         slot_bar += 8u;
         if (slot_bar == 8u * kDecSlots) {
           slot_bar = 0;
@@ -624,7 +617,10 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
           next_stage();
         }
         // ---- end of the segment: wait for its last MMAs.
-        if (bad == 0) ptx::mbar_wait_sticky(last_bar, last_ph, abort_addr, bad);
+        // (the slot stored last is the one before the current ring position)
+        const uint32_t last_bar = slot_bar == 0 ? 8u * (kDecSlots - 1) : slot_bar - 8u;
+        const uint32_t last_ph = slot_bar == 0 ? slot_ph ^ 1u : slot_ph;
+        ptx::mbar_wait_sticky(afree0 + last_bar, last_ph, abort_addr, bad);
       }
       // Drain the accumulator.  A warp that has given up skips the work but still meets
       // its siblings at the named barriers of a stream-K slice, here and for every
