@@ -97,6 +97,7 @@ def _apply_env_options(lib: ctypes.CDLL) -> None:
         ("CHORD_B200_PREGATHER", "pregather"),
         ("CHORD_B200_DECODE_KERNEL", "decode_kernel"),
         ("CHORD_B200_PDL", "pdl"),
+        ("CHORD_B200_NPAIR", "npair"),
     ):
         value = os.environ.get(env)
         if value is None:

@@ -68,6 +68,7 @@ struct Options {
   int contiguous_tile = 0; // 0 / 256 = merge neighbouring 128-row blocks of one expert; 128 = do not
   int a_stages = 0;        // 0 = automatic; depth of the TMEM operand ring (2..7)
   int pregather = 1;       // 1 = `indexed` with blocks of >= 64 rows copies the routed rows into slot order first
+  int npair = 1;           // 1 = tiles of <= 128 tokens with consecutive activation rows span two 128-row weight blocks
   int ksplit = 1;          // 1 = layouts with one MMA issuer split small tiles' K halves over two issuers
   int decode_kernel = 1;   // 1 = token tiles of <= 32 rows (indexed, masked) use the warpgroup-per-worker kernel; 0 = never
   int max_stages = 0;      // 0 = as many as fit

@@ -90,6 +90,9 @@ int chord_b200_set_option(const char* name, int64_t value) {
   } else if (!std::strcmp(name, "ksplit")) {
     if (value != 0 && value != 1) return fail(kInvalidArgument, "ksplit must be 0 or 1");
     o.ksplit = static_cast<int>(value);
+  } else if (!std::strcmp(name, "npair")) {
+    if (value != 0 && value != 1) return fail(kInvalidArgument, "npair must be 0 or 1");
+    o.npair = static_cast<int>(value);
   } else if (!std::strcmp(name, "decode_kernel")) {
     if (value != 0 && value != 1) return fail(kInvalidArgument, "decode_kernel must be 0 or 1");
     o.decode_kernel = static_cast<int>(value);

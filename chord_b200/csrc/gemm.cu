@@ -184,7 +184,9 @@ gather_routed_rows_kernel(const __nv_bfloat16* __restrict__ x, const int32_t* __
 // Workspace of an `indexed` launch: the stream-K partials, then (1024-byte aligned) the
 // slot-ordered copy of the activations when the routing blocks are large enough for it.
 int64_t stream_k_bytes(int grid, int mma_n) {
-  const int64_t general = static_cast<int64_t>(grid) * kBlockN * mma_n * 4;
+  // one FP32 slot of 128 x mma_n per CTA; tiles of at most 128 tokens may span two weight
+  // blocks (two accumulators), which doubles the slot
+  const int64_t general = static_cast<int64_t>(grid) * kBlockN * mma_n * 4 * (mma_n <= 128 ? 2 : 1);
   return (general + 1023) / 1024 * 1024;
 }
 
@@ -319,6 +321,21 @@ int launch_gemm(GemmParams p, const void* x, const int32_t* packed, const void* 
   // same 256 columns).  Not where two warps gather the rows: there the 128-token layout
   // keeps its double-buffered accumulator instead, which measured 7 % faster.
   p.ksplit = (p.issuers == 1 && options().ksplit != 0 && p.x_load == kXLoadTiled) ? 1 : 0;
+  // Tiles of at most 128 tokens with consecutive activation rows take two neighbouring
+  // 128-row weight blocks each (one issuer, dequant group and accumulator per block), so
+  // that an activation stage is fetched from L2 once per 256 weight rows.  Needs the
+  // doubled scratch slot; a caller that sized its workspace for single-block tiles (the
+  // built-in 5 MiB scratch with 64-row blocks) gets those.
+  const int64_t slot_bytes = static_cast<int64_t>(grid) * kBlockN * p.mma_n * 4;
+  const int64_t behind_partials = gathered != nullptr ? static_cast<int64_t>(p.sorted_len) * p.k * 2 : 0;
+  p.npair = (options().npair != 0 && p.x_load == kXLoadTiled && p.mma_n <= 128 &&
+             (p.n / kBlockN) % 2 == 0 &&
+             workspace_bytes >= (gathered != nullptr ? stream_k_bytes(grid, p.mma_n) + behind_partials
+                                                     : 2 * slot_bytes)) ? 1 : 0;
+  if (p.npair) {
+    p.issuers = 2;
+    p.ksplit = 0;
+  }
   const int acc_cols = p.ksplit ? 256 : p.issuers * p.mma_n;
   p.a_stages = 2 * acc_cols <= 128 ? 6 : 4;
   if (options().a_stages > 0 && (512 - 64 * options().a_stages) >= acc_cols) {
@@ -340,7 +357,7 @@ int launch_gemm(GemmParams p, const void* x, const int32_t* packed, const void* 
   CHORD_REQUIRE(p.locks != nullptr && num_locks >= grid,
                 "stream-K needs a zeroed locks buffer of at least %d lock words, got %lld", grid,
                 static_cast<long long>(num_locks));
-  const int64_t need = static_cast<int64_t>(grid) * kBlockN * p.mma_n * 4;
+  const int64_t need = slot_bytes * (p.npair ? 2 : 1);
   CHORD_REQUIRE(p.workspace != nullptr && workspace_bytes >= need,
                 "workspace must hold %lld bytes, got %lld", static_cast<long long>(need),
                 static_cast<long long>(workspace_bytes));
@@ -452,7 +469,7 @@ int64_t chord_b200_gemm_workspace_bytes(int64_t tile_tokens) {
   const int grid = chord::grid_size(dev);
   const int mma_n = chord::round_up16(tile_tokens);
   if (mma_n <= chord::kDecMaxTokens) return chord::decode_workspace_bytes(grid, mma_n);
-  return static_cast<int64_t>(grid) * chord::kBlockN * mma_n * 4;
+  return chord::stream_k_bytes(grid, mma_n);
 }
 
 int64_t chord_b200_indexed_workspace_bytes(int64_t block_m, int64_t sorted_len, int64_t k) {
@@ -616,11 +633,15 @@ int chord_b200_contiguous(const void* x, const int32_t* packed, const void* scal
   p.out_rows = static_cast<int32_t>(m);
   CHORD_REQUIRE(m / 128 <= chord::kMaxMTiles && num_experts <= 0x7FFF,
                 "contiguous supports at most %d rows and %d experts", chord::kMaxMTiles * 128, 0x7FFF);
-  // Token tiles are 128-row blocks, merged in pairs where two neighbours belong to one
-  // expert (option contiguous_tile = 128 switches the merging off).
+  // Token tiles are the 128-row blocks, each spanning two 128-row weight blocks
+  // (`npair`).  Where that layout does not apply (option npair = 0, an odd number of
+  // weight blocks) or with option contiguous_tile = 256, neighbouring blocks of one
+  // expert are merged into 256-token tiles over one weight block instead.
   {
     chord::OptionsReadLock options_guard(chord::options_mutex());
-    p.tile_tokens = chord::options().contiguous_tile == 128 ? 128 : 256;
+    const chord::Options& o = chord::options();
+    const bool pairs = o.npair != 0 && (n / chord::kBlockN) % 2 == 0;
+    p.tile_tokens = o.contiguous_tile == 128 || (o.contiguous_tile == 0 && pairs) ? 128 : 256;
   }
   p.top_k = 1;
   p.m_blocks = static_cast<int32_t>(m / 128);

@@ -124,6 +124,7 @@ struct GemmParams {
   int32_t x_stages;     // depth of the activation ring
   int32_t issuers;      // 1, 2 or 4 MMA issuers (and accumulators)
   int32_t ksplit;       // single-issuer layouts: a second issuer takes the second K half of tiles of <= 128 tokens
+  int32_t npair;        // 1 = a tile is two neighbouring 128-row weight blocks sharing one activation stage (tiles of <= 128 tokens)
   int32_t a_stages;     // depth of the TMEM A ring; accumulators start at column 64 * a_stages
   int32_t num_locks;
   int32_t pdl;          // host side only: launch with the programmatic stream-serialization attribute
@@ -263,9 +264,10 @@ struct __align__(16) GemmShared {
 __device__ __forceinline__ TileInfo decode_tile(const GemmParams& p, const GemmShared& sh,
                                                 int32_t tile) {
   TileInfo t;
-  const int32_t n_blocks = p.n / kBlockN;
+  // With `npair` a tile spans two neighbouring 128-row weight blocks (n0 and n0 + 128).
+  const int32_t n_blocks = p.n / (kBlockN << p.npair);
   const int32_t mb = tile / n_blocks;
-  t.n0 = (tile - mb * n_blocks) * kBlockN;
+  t.n0 = (tile - mb * n_blocks) * (kBlockN << p.npair);
   t.m0 = 0;
   t.limit = 0;
   t.mma_n = p.mma_n;
@@ -458,6 +460,14 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
   // thread ~100 cycles on a busy SM whatever its size, so a lone issuer caps small
   // tiles at ~900 cycles per stage.
   const bool ksplit = p.ksplit != 0;
+  // `npair`: two issuers as well, but issuer i (with dequant group i) owns the weight block
+  // n0 + 128 i of the tile: weight/scale stages alternate between the two blocks, one
+  // activation stage serves both, and the two accumulators are two output blocks instead
+  // of two partial sums.  An activation tile then crosses from L2 to the SM once per 256
+  // weight rows instead of once per 128: with 128-row tiles the kernel was bound by that
+  // traffic (about 10 TB/s between L2 and the SMs), not by the tensor pipe.
+  const bool npair = p.npair != 0;
+  const int32_t w_per_kb = npair ? 2 : 1;  // weight/scale ring entries per K block
   // 256-token layouts with consecutive activation rows: sub-slot ring (see XSubRing).
   const bool subslots = ksplit && p.x_load == kXLoadTiled && p.mma_n == 256;
   constexpr uint32_t kSubBytes = 128u * 256u;
@@ -482,7 +492,7 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
     const uint32_t xfull_count = p.x_load == kXLoadCpAsync ? kHelperThreads / 32 : 1u;
     for (uint32_t s = 0; s < (subslots ? 2u * x_stages : x_stages); ++s) {
       ptx::mbar_init(ptx::smem_u32(&sh.xfull[s]), xfull_count);
-      ptx::mbar_init(ptx::smem_u32(&sh.xempty[s]), ksplit ? 2 : 1);
+      ptx::mbar_init(ptx::smem_u32(&sh.xempty[s]), (ksplit || npair) ? 2 : 1);
     }
     for (uint32_t a = 0; a < 2 * a_stages; ++a) {
       ptx::mbar_init(ptx::smem_u32(&sh.afull[a]), 4);
@@ -587,7 +597,7 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
 
   const uint32_t tmem_base = __shfl_sync(0xffffffffu, sh.tmem_base, 0);  // uniform, see `warp`
   volatile uint32_t* abort_flag = &sh.abort_flag;
-  const int32_t tiles = __shfl_sync(0xffffffffu, sh.m_blocks, 0) * (p.n / kBlockN);
+  const int32_t tiles = __shfl_sync(0xffffffffu, sh.m_blocks, 0) * (p.n / (kBlockN << p.npair));
   SegmentIterator iter;
   iter.init(tiles, k_iters, static_cast<int32_t>(gridDim.x), static_cast<int32_t>(blockIdx.x));
   Segment seg;
@@ -607,17 +617,20 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
         const TileInfo t = decode_tile(p, sh, seg.tile);
         if (!t.valid) continue;
         const int32_t col = weights ? 2 * t.n0 : t.n0;
+        const int32_t col_step = weights ? 2 * kBlockN : kBlockN;  // to the tile's second weight block
         int32_t row = t.expert * rows_per_expert + seg.kb * rows_per_stage;
-        for (int32_t kb = seg.kb; kb < seg.ke; ++kb) {
-          if (!ptx::mbar_wait(ptx::smem_u32(&sh.wempty[cur.s]), cur.ph ^ 1u, abort_flag)) {
-            ok = false;
-            break;
+        for (int32_t kb = seg.kb; ok && kb < seg.ke; ++kb) {
+          for (int32_t sub = 0; sub < w_per_kb; ++sub) {
+            if (!ptx::mbar_wait(ptx::smem_u32(&sh.wempty[cur.s]), cur.ph ^ 1u, abort_flag)) {
+              ok = false;
+              break;
+            }
+            const uint32_t full = ptx::smem_u32(&sh.wfull[cur.s]);
+            ptx::mbar_arrive_expect_tx(full, stage_bytes);
+            ptx::tma_load_2d(ptx::smem_u32(ring + cur.s * stage_bytes), map, full, col + sub * col_step, row);
+            cur.advance(w_stages);
           }
-          const uint32_t full = ptx::smem_u32(&sh.wfull[cur.s]);
-          ptx::mbar_arrive_expect_tx(full, stage_bytes);
-          ptx::tma_load_2d(ptx::smem_u32(ring + cur.s * stage_bytes), map, full, col, row);
           row += rows_per_stage;
-          cur.advance(w_stages);
         }
       }
       if (!ok) {
@@ -856,7 +869,40 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
         uint32_t acc = 0;
         const bool split = ksplit && t.mma_n <= 128;
         for (int32_t kb = seg.kb; kb < seg.ke; ++kb, ++it) {
-          if (ksplit) {
+          if (npair) {
+            // The K block's two operand-ring entries belong to the tile's two weight blocks;
+            // this issuer takes the one of its block, with both K halves, into its accumulator.
+            uint32_t as = acur.s + me, aph = acur.ph;
+            if (as >= a_stages) {
+              as -= a_stages;
+              aph ^= 1u;
+            }
+            const uint32_t a = as << 1;
+            if (!ptx::mbar_wait(ptx::smem_u32(&sh.xfull[cur.s]), cur.ph, abort_flag)) {
+              ok = false;
+              break;
+            }
+            const uint32_t a_addr = tmem_base + as * kAColsPerStage;
+            if (!ptx::mbar_wait(ptx::smem_u32(&sh.afull[a]), aph, abort_flag)) {
+              ok = false;
+              break;
+            }
+            ptx::tc_fence_after();
+            ptx::mma_ts_k64(d_addr, a_addr, xdesc, idesc, acc);
+            ptx::mma_commit(ptx::smem_u32(&sh.aempty[a]));
+            if (!ptx::mbar_wait(ptx::smem_u32(&sh.afull[a + 1]), aph, abort_flag)) {
+              ok = false;
+              break;
+            }
+            ptx::tc_fence_after();
+            if (!(k_tail_half && kb == k_iters - 1)) {
+              ptx::mma_ts_k64(d_addr, a_addr + 32, xdesc + xdesc_half, idesc, 1);
+            }
+            acc = 1;
+            ptx::mma_commit(ptx::smem_u32(&sh.aempty[a + 1]));
+            ptx::mma_commit(ptx::smem_u32(&sh.xempty[cur.s]));
+            acur.advance(a_stages);  // the other block's entry; the common advance below takes this one
+          } else if (ksplit) {
             const uint32_t a = acur.s << 1;
             const uint32_t aph = acur.ph;
             uint32_t xslot = cur.s;       // barrier (and, with sub-slots, buffer) of this stage
@@ -1030,7 +1076,7 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
       if (!t.valid) continue;
       // This group owns the stages whose running index is `group` modulo the number
       // of groups: step over the others without visiting them.
-      const uint32_t seg_len = static_cast<uint32_t>(seg.ke - seg.kb);
+      const uint32_t seg_len = static_cast<uint32_t>((seg.ke - seg.kb) * w_per_kb);  // ring entries
       const uint32_t first = (group - it) & (kDequantGroups - 1);
       const uint32_t it_end = it + seg_len;
       if (first >= seg_len) {
@@ -1094,7 +1140,8 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
     const uint32_t et = threadIdx.x - kFirstEpilogueWarp * 32;  // 0..127 == TMEM lane
     uint32_t segc = 0, it0 = 0;
     bool ok = true;
-    const size_t ws_slot = static_cast<size_t>(kBlockN) * p.mma_n;
+    const size_t ws_block = static_cast<size_t>(kBlockN) * p.mma_n;  // partial sums of one weight block
+    const size_t ws_slot = ws_block * w_per_kb;
     while (ok && iter.next(seg)) {
       const TileInfo t = decode_tile(p, sh, seg.tile);
       if (!t.valid) continue;
@@ -1129,10 +1176,14 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
         break;
       }
       const uint32_t d_addr = tmem_base + ((q * 32u) << 16) + d_col0 + d * ni * d_cols;
-      __nv_bfloat16* out_tile = p.out + t.n0 + q * 32;
       // Issuer i accumulated the stages it0 + j with (it0 + j) % ni == i; it took part
-      // in this segment only if one of them falls inside it.
+      // in this segment only if one of them falls inside it.  (With `npair` accumulator
+      // `sub` is the tile's weight block `sub` instead, and nothing is summed.)
       const uint32_t seg_len = static_cast<uint32_t>(seg.ke - seg.kb);
+      for (int32_t sub = 0; sub < w_per_kb; ++sub) {
+      const int32_t n_sub = t.n0 + sub * kBlockN + static_cast<int32_t>(q) * 32;
+      __nv_bfloat16* out_tile = p.out + n_sub;
+      const size_t ws_sub = static_cast<size_t>(sub) * ws_block;
       for (int32_t c0 = 0; c0 < row_slots; c0 += 16) {
         float acc[16];
 #pragma unroll
@@ -1142,7 +1193,9 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
         const bool computed = c0 < t.mma_n;
         if (!computed && seg.type == kSegContrib) continue;
         for (uint32_t i = 0; computed && i < ni; ++i) {
-          if (ksplit) {
+          if (npair) {
+            if (static_cast<int32_t>(i) != sub) continue;
+          } else if (ksplit) {
             // issuer 1 holds the second K halves of tiles of at most 128 tokens, unless the
             // segment is nothing but the half-filled last stage
             if (i == 1 && (t.mma_n > 128 || seg_len == (k_tail_half && seg.ke == k_iters ? 1u : 0u))) continue;
@@ -1156,14 +1209,14 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
           for (int j = 0; j < 16; ++j) acc[j] += __uint_as_float(v[j]);
         }
         if (seg.type == kSegContrib) {
-          float* dst = p.workspace + blockIdx.x * ws_slot + static_cast<size_t>(c0) * kBlockN + et;
+          float* dst = p.workspace + blockIdx.x * ws_slot + ws_sub + static_cast<size_t>(c0) * kBlockN + et;
 #pragma unroll
           for (int j = 0; j < 16; ++j) __stcg(dst + j * kBlockN, acc[j]);
           continue;
         }
         if (seg.type == kSegOwner && computed) {
           for (int32_t peer = 1; peer <= seg.peer; ++peer) {
-            const float* src = p.workspace + (blockIdx.x + peer) * ws_slot +
+            const float* src = p.workspace + (blockIdx.x + peer) * ws_slot + ws_sub +
                                static_cast<size_t>(c0) * kBlockN + et;
 #pragma unroll
             for (int j = 0; j < 16; ++j) acc[j] += __ldcg(src + j * kBlockN);
@@ -1187,13 +1240,14 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
               // the row lives wherever the caller's table says (possibly on another GPU)
               __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(
                   __ldg(reinterpret_cast<const unsigned long long*>(p.out_row_ptr) + row));
-              if (dst != nullptr) *reinterpret_cast<uint4*>(dst + t.n0 + q * 32 + piece * 8) = v;
+              if (dst != nullptr) *reinterpret_cast<uint4*>(dst + n_sub + piece * 8) = v;
             } else {
               *reinterpret_cast<uint4*>(out_tile + static_cast<size_t>(row) * p.n + piece * 8) = v;
             }
           }
         }
         __syncwarp();
+      }
       }
       // Release the accumulator buffer to the MMA issuer.
       ptx::tc_fence_before();

@@ -50,13 +50,17 @@ const char* chord_b200_version(void);
  *                     helper warps (default), 1 TMA tile::gather4
  *   "dequant_groups"  2 (default) or 4 groups of four dequantising warps
  *   "issuers"         0 automatic (default); 1, 2 or 4 MMA-issuing threads
- *   "contiguous_tile" 0 / 256 merge neighbouring 128-row blocks of one expert
- *                     (default), 128 do not
+ *   "contiguous_tile" 0 automatic (default: 128-token tiles over two weight blocks
+ *                     where "npair" applies, else 256); 128; 256 = merge neighbouring
+ *                     128-row blocks of one expert into 256-token tiles
  *   "a_stages"        0 automatic (default); 2..7 depth of the tensor-memory operand ring
  *   "pregather"       1 (default) `indexed` with blocks of 64 rows or more first copies
  *                     the routed rows into slot order; 0 gathers inside the kernel
  *   "ksplit"          1 (default) single-issuer layouts give the second K half of tiles
  *                     of at most 128 tokens to a second issuer; 0 off
+ *   "npair"           1 (default) tiles of at most 128 tokens with consecutive activation
+ *                     rows span two neighbouring 128-row weight blocks, so that an
+ *                     activation stage is fetched once per 256 weight rows; 0 one block
  *   "decode_kernel"   1 (default) token tiles of at most 32 rows (indexed, masked) run
  *                     the warpgroup-per-worker kernel; 0 always the general kernel
  *   "max_stages"      0 as many shared-memory stages as fit (default), else a cap

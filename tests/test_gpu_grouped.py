@@ -143,14 +143,15 @@ def test_grouped_argument_checks(device):
                               torch.zeros(64, dtype=torch.int32, device=device))
 
 
-@pytest.mark.parametrize("option,value", [("ksplit", 0), ("contiguous_tile", 128), ("decode_kernel", 0)])
+@pytest.mark.parametrize("option,value", [("ksplit", 0), ("contiguous_tile", 256), ("npair", 0), ("decode_kernel", 0)])
 def test_grouped_kernel_variants(device, option, value):
-    """Without the second MMA issuer / without merged 256-token tiles / with small masked
-    tiles on the general kernel: same results within tolerance."""
+    """Without the second MMA issuer / with merged 256-token tiles over one weight block /
+    with one weight block per tile / with small masked tiles on the general kernel: same
+    results within tolerance."""
     import chord_b200
     from chord_b200 import _lib
 
-    defaults = {"ksplit": 1, "contiguous_tile": 0, "decode_kernel": 1}
+    defaults = {"ksplit": 1, "contiguous_tile": 0, "npair": 1, "decode_kernel": 1}
     ccase = make_contiguous_case([5, 300, 0, 128, 77, 513], 512, 640, seed=31)
     mcase = make_masked_case(6, 200, 256, 384, 16, seed=32)
     mcase["masked_m"] = torch.tensor([0, 3, 16, 33, 150, 200], dtype=torch.int32)
