@@ -190,6 +190,17 @@ class DecodeWorkload:
         if events:
             events[3].record()
 
+    def step_fused(self):
+        """The same step with SiLU*mul in gate_up's epilogue (two launches).  Measured
+        beside `step`: at these tile sizes it is the slower of the two."""
+        import chord_b200
+
+        routing = (self.sorted_ids, self.expert_ids, self.padded)
+        chord_b200.indexed_gate_up_silu(self.x, self.w13, *routing, TOP_K, locks=self.locks,
+                                        outputs=self.hidden, block_m=self.block_m)
+        chord_b200.indexed(self.hidden, self.w2, *routing, 1, locks=self.locks, outputs=self.out,
+                           block_m=self.block_m)
+
     def step_e2e(self):
         """Same step through the public API from host buffers."""
         self.x.copy_(self.x_host, non_blocking=True)
@@ -357,36 +368,47 @@ def _metrics(got, ref):
 def decode_parity(workload, kept13, kept2):
     """The benchmarked step's outputs against the CPU oracle on the experts in `kept13`
     (checkpoint words and scales kept on the host): gate_up from the activations, down
-    from the kernel's own SiLU*mul output; and exactly the local routes are written."""
+    from the kernel's own SiLU*mul output, the fused gate_up + SiLU*mul launch against
+    silu(gate) * up of the oracle's FP32 result; and exactly the local routes are written."""
     nan = float("nan")
-    workload.gate_up.fill_(nan)
-    workload.hidden.fill_(nan)
-    workload.out.fill_(nan)
+    for buf in (workload.gate_up, workload.hidden, workload.out):
+        buf.fill_(nan)
     workload.step()
     torch.cuda.synchronize()
     flat = workload.topk.reshape(-1)
     local = flat < LOCAL_EXPERTS
     gate_up, hidden, out = workload.gate_up.float().cpu(), workload.hidden.cpu(), workload.out.float().cpu()
-    rows_ok = all(torch.equal(~torch.isnan(buf).any(dim=1), local)
-                  for buf in (gate_up, hidden.float(), out))
-    worst = {"gate_up": [0.0, 0.0], "down": [0.0, 0.0]}
+    rows_ok = all(torch.equal(~torch.isnan(buf).any(dim=1), local) for buf in (gate_up, hidden.float(), out))
+    workload.hidden.fill_(nan)
+    workload.step_fused()
+    torch.cuda.synchronize()
+    fused = workload.hidden.float().cpu()
+    rows_ok = rows_ok and torch.equal(~torch.isnan(fused).any(dim=1), local)
+    worst = {"gate_up": [0.0, 0.0], "down": [0.0, 0.0], "gate_up_silu_fused": [0.0, 0.0]}
     x = workload.x_host
     for e in sorted(kept13):
         rows = torch.where(flat == e)[0]
         if rows.numel() == 0:
             continue
         tokens = torch.div(rows, TOP_K, rounding_mode="floor")
+        ref13 = x[tokens].float() @ dequantized_f32(*kept13[e]).t()
+        act = torch.nn.functional.silu(ref13[:, :INTER]) * ref13[:, INTER:]
         for name, got, ref in (
-            ("gate_up", gate_up[rows], x[tokens].float() @ dequantized_f32(*kept13[e]).t()),
+            ("gate_up", gate_up[rows], ref13),
             ("down", out[rows], hidden[rows].float() @ dequantized_f32(*kept2[e]).t()),
+            ("gate_up_silu_fused", fused[rows], act),
         ):
             cos, rel = _metrics(got, ref)
             worst[name] = [max(worst[name][0], cos), max(worst[name][1], rel)]
-    ok = rows_ok and all(v[0] <= COS_LIMIT and v[1] <= REL_LIMIT for v in worst.values())
-    return {"checked_experts": sorted(kept13), "rows_written_match_routing": rows_ok,
-            "gate_up": {"cos_diff": worst["gate_up"][0], "max_abs_rel": worst["gate_up"][1]},
-            "down": {"cos_diff": worst["down"][0], "max_abs_rel": worst["down"][1]},
-            "limits": {"cos_diff": COS_LIMIT, "max_abs_rel": REL_LIMIT}, "ok": bool(ok)}
+    ok = rows_ok and all(worst[n][0] <= COS_LIMIT and worst[n][1] <= REL_LIMIT for n in ("gate_up", "down"))
+    ok = ok and worst["gate_up_silu_fused"][0] <= COS_LIMIT and worst["gate_up_silu_fused"][1] <= CHAIN_REL_LIMIT
+    result = {"checked_experts": sorted(kept13), "rows_written_match_routing": bool(rows_ok)}
+    for name, (cos, rel) in worst.items():
+        result[name] = {"cos_diff": cos, "max_abs_rel": rel}
+    result["limits"] = {"cos_diff": COS_LIMIT, "max_abs_rel": REL_LIMIT,
+                        "max_abs_rel_after_activation": CHAIN_REL_LIMIT}
+    result["ok"] = bool(ok)
+    return result
 
 
 # --------------------------------------------------------------- CPU baseline --
@@ -792,6 +814,7 @@ def main():
     with ClockSampler(local_rank) as sampler:
         ms = time_region(workload.step, args.steps, args.warmup, world, device)
         kernel_us = time_kernels(workload, max(args.steps, 5))
+        fused_us = time_region(workload.step_fused, args.steps, args.warmup, world, device) * 1e3
         e2e_ms = time_region(lambda: (workload.step_e2e(), torch.cuda.synchronize()), args.steps,
                              args.warmup, world, device)
     clocks = sampler.summary()
@@ -847,6 +870,7 @@ def main():
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": workload_config(args.batch, pdl),
             "kernels_us": {"gate_up": kernel_us[0], "silu_mul": kernel_us[1], "down": kernel_us[2]},
+            "fused_gate_up_silu_step_us": fused_us,
             "routing": {k: facts[k] for k in ("block_m", "active_experts", "routed_rows")},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                          "frac": achieved / peaks["hbm_gbs"], "peak_kind": peaks["kind"],

@@ -27,6 +27,7 @@ _EXPORTS = {
     "silu_mul": "chord_b200.fused_ops",
     "moe_align_block_size": "chord_b200.fused_ops",
     "check_status": "chord_b200.indexed_gemm",
+    "indexed_gate_up_silu": "chord_b200.indexed_gemm",
     "set_option": "chord_b200._lib",
 }
 

@@ -16,10 +16,18 @@ import torch
 SUPPORTED_COMPUTE_CAPABILITY_MAJOR = 10
 
 
+_CHECKED_DEVICES: set = set()
+
+
 def supported_gpu(device: torch.device) -> None:
     """This build runs on compute capability 10.x only (the reference gates on
-    9.0 / 10.0 / 10.3, packing.py:16-23)."""
+    9.0 / 10.0 / 10.3, packing.py:16-23).  The verdict is remembered per device: the
+    query costs microseconds on a path that is called once per GEMM."""
+    if device in _CHECKED_DEVICES:
+        return
     major, minor = torch.cuda.get_device_capability(device)
+    if major == SUPPORTED_COMPUTE_CAPABILITY_MAJOR:
+        _CHECKED_DEVICES.add(device)
     if major != SUPPORTED_COMPUTE_CAPABILITY_MAJOR:
         raise RuntimeError(
             "chord_b200 W4A16 kernels require an SM100/SM103 Blackwell GPU, got compute "

@@ -37,6 +37,11 @@ SIGNATURES = {
                                   _ptr, _i64, _ptr, _i64, _i64, _i64, _i64, _i64, _i64, _ptr]),
     "chord_b200_indexed_rows": (_int, [_ptr, _ptr, _ptr, _ptr, _i64, _ptr, _i64, _ptr, _ptr, _ptr, _i64,
                                        _ptr, _i64, _ptr, _i64, _i64, _i64, _i64, _i64, _i64, _ptr]),
+    "chord_b200_indexed_gate_up_silu": (_int, [_ptr, _ptr, _ptr, _ptr, _i64, _ptr, _i64, _ptr, _ptr, _ptr,
+                                               _i64, _ptr, _i64, _ptr, _i64, _i64, _i64, _i64, _i64, _i64,
+                                               _ptr]),
+    "chord_b200_gate_up_silu_supported": (_int, [_i64, _i64, _i64]),
+    "chord_b200_gate_up_silu_workspace_bytes": (_i64, [_i64, _i64, _i64]),
     "chord_b200_indexed_static_scratch": (_int, [_ptr, _ptr, _ptr, _ptr, _i64, _ptr, _i64, _ptr, _ptr,
                                                  _ptr, _i64, _ptr, _i64, _i64, _i64, _i64, _i64, _i64,
                                                  _ptr]),
@@ -121,11 +126,44 @@ def check(code: int) -> None:
     raise RuntimeError(message)
 
 
+_OPTIONS_EPOCH = 0
+
+
+def options_epoch() -> int:
+    """Changes whenever an option is set through this module (scratch sizes depend on
+    some options, so caches of them are keyed by it)."""
+    return _OPTIONS_EPOCH
+
+
 def set_option(name: str, value: int) -> None:
+    global _OPTIONS_EPOCH
     check(load().chord_b200_set_option(name.encode(), int(value)))
+    _OPTIONS_EPOCH += 1
 
 
 def stream_handle(device) -> int:
     import torch
 
     return torch.cuda.current_stream(device).cuda_stream
+
+
+class on_device:
+    """``with on_device(device):`` makes ``device`` current for the C-ABI calls inside;
+    when it already is (the common case) nothing is switched, which saves the several
+    microseconds a ``torch.cuda.device`` round trip costs per GEMM call."""
+
+    __slots__ = ("guard",)
+
+    def __init__(self, device):
+        import torch
+
+        index = device.index
+        self.guard = None if index is None or index == torch.cuda.current_device() else torch.cuda.device(device)
+
+    def __enter__(self):
+        if self.guard is not None:
+            self.guard.__enter__()
+
+    def __exit__(self, *exc):
+        if self.guard is not None:
+            self.guard.__exit__(*exc)

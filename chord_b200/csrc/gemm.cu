@@ -236,14 +236,23 @@ int launch_decode(GemmParams p, const DeviceInfo& dev, const int32_t* packed, co
   CHORD_CUDA(cudaGetDevice(&device));
   std::call_once(flags[device & 63], [&] {
     attr_result[device & 63] = cudaFuncSetAttribute(
-        w4a16_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, dev.max_smem_optin);
+        w4a16_decode_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, dev.max_smem_optin);
+    if (attr_result[device & 63] == cudaSuccess) {
+      attr_result[device & 63] = cudaFuncSetAttribute(
+          w4a16_decode_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, dev.max_smem_optin);
+    }
   });
   if (attr_result[device & 63] != cudaSuccess) {
     return fail(kCudaError, "cudaFuncSetAttribute failed: %s",
                 cudaGetErrorString(attr_result[device & 63]));
   }
-  CHORD_CUDA(launch_kernel(w4a16_decode_kernel, dim3(grid), dim3(kDecThreads), smem, stream,
-                           p.pdl != 0, tm_w, tm_s, p));
+  if (p.fuse_silu) {
+    CHORD_CUDA(launch_kernel(w4a16_decode_kernel<true>, dim3(grid), dim3(kDecThreads), smem, stream,
+                             p.pdl != 0, tm_w, tm_s, p));
+  } else {
+    CHORD_CUDA(launch_kernel(w4a16_decode_kernel<false>, dim3(grid), dim3(kDecThreads), smem, stream,
+                             p.pdl != 0, tm_w, tm_s, p));
+  }
   return kOk;
 }
 
@@ -284,8 +293,13 @@ int launch_gemm(GemmParams p, const void* x, const int32_t* packed, const void* 
   if (options().pdl != 0) p.pdl = 1;
   // The decode kernel runs when the caller's locks and scratch are large enough for
   // one per warpgroup; with the smaller buffers of the general kernel, that one runs.
+  // SiLU*mul fused into the gate_up epilogue: on the decode kernel for 16-token tiles (two
+  // accumulators of 16 columns: twice the scratch slot), on the general kernel for tiles that
+  // span a gate and an up block (`npair` layout).
+  const bool fused_decode_ok = p.mma_n == 16 && p.k % kDecStageK == 0;
   if (decode_kernel_applies(p) && offsets_fit && p.locks != nullptr && p.workspace != nullptr &&
-      num_locks >= decode_workers(grid) && workspace_bytes >= decode_workspace_bytes(grid, p.mma_n)) {
+      (!p.fuse_silu || fused_decode_ok) && num_locks >= decode_workers(grid) &&
+      workspace_bytes >= decode_workspace_bytes(grid, p.mma_n) * (p.fuse_silu ? 2 : 1)) {
     p.num_locks = static_cast<int32_t>(num_locks);
     return launch_decode(p, dev, packed, scale, grid, static_cast<cudaStream_t>(stream));
   }
@@ -328,7 +342,7 @@ int launch_gemm(GemmParams p, const void* x, const int32_t* packed, const void* 
   // built-in 5 MiB scratch with 64-row blocks) gets those.
   const int64_t slot_bytes = static_cast<int64_t>(grid) * kBlockN * p.mma_n * 4;
   const int64_t behind_partials = gathered != nullptr ? static_cast<int64_t>(p.sorted_len) * p.k * 2 : 0;
-  p.npair = (options().npair != 0 && p.x_load == kXLoadTiled && p.mma_n <= 128 &&
+  p.npair = ((options().npair != 0 || p.fuse_silu) && p.x_load == kXLoadTiled && p.mma_n <= 128 &&
              (p.n / kBlockN) % 2 == 0 &&
              workspace_bytes >= (gathered != nullptr ? stream_k_bytes(grid, p.mma_n) + behind_partials
                                                      : 2 * slot_bytes)) ? 1 : 0;
@@ -336,6 +350,10 @@ int launch_gemm(GemmParams p, const void* x, const int32_t* packed, const void* 
     p.issuers = 2;
     p.ksplit = 0;
   }
+  CHORD_REQUIRE(!p.fuse_silu || p.npair,
+                "gate_up with fused SiLU*mul needs routing blocks of at most 16 rows, or of 64 to 128 "
+                "rows with the full workspace of chord_b200_indexed_workspace_bytes(); got block_m=%d",
+                p.tile_tokens);
   const int acc_cols = p.ksplit ? 256 : p.issuers * p.mma_n;
   p.a_stages = 2 * acc_cols <= 128 ? 6 : 4;
   if (options().a_stages > 0 && (512 - 64 * options().a_stages) >= acc_cols) {
@@ -472,6 +490,13 @@ int64_t chord_b200_gemm_workspace_bytes(int64_t tile_tokens) {
   return chord::stream_k_bytes(grid, mma_n);
 }
 
+int64_t chord_b200_gate_up_silu_workspace_bytes(int64_t block_m, int64_t sorted_len, int64_t k) {
+  const int64_t plain = chord_b200_indexed_workspace_bytes(block_m, sorted_len, k);
+  if (plain < 0) return plain;
+  // 16-token tiles keep two accumulators per worker: twice the scratch slot
+  return chord::round_up16(block_m) <= chord::kDecMaxTokens ? 2 * plain : plain;
+}
+
 int64_t chord_b200_indexed_workspace_bytes(int64_t block_m, int64_t sorted_len, int64_t k) {
   chord::OptionsReadLock options_guard(chord::options_mutex());
   chord::DeviceInfo dev;
@@ -526,7 +551,8 @@ static int indexed_launch(const void* x, const int32_t* packed, const void* scal
                           int64_t expert_len, const int32_t* num_tokens_padded, void* out,
                           void* const* out_rows, int32_t* locks, int64_t num_locks, void* workspace,
                           int64_t workspace_bytes, int32_t* status, int64_t m, int64_t n, int64_t k,
-                          int64_t num_experts, int64_t top_k, int64_t block_m, void* stream) {
+                          int64_t num_experts, int64_t top_k, int64_t block_m, void* stream,
+                          int fuse_silu = 0) {
   CHORD_REQUIRE(m > 0, "inputs must be non-empty, got m=%lld", static_cast<long long>(m));
   CHORD_REQUIRE(top_k > 0, "top_k must be positive, got %lld", static_cast<long long>(top_k));
   CHORD_REQUIRE(block_m > 0 && block_m % 8 == 0 && block_m <= chord::kMaxTileTokens,
@@ -553,6 +579,7 @@ static int indexed_launch(const void* x, const int32_t* packed, const void* scal
   p.x = static_cast<const __nv_bfloat16*>(x);
   p.out = static_cast<__nv_bfloat16*>(out);
   p.out_row_ptr = out_rows;
+  p.fuse_silu = fuse_silu;
   p.workspace = static_cast<float*>(workspace);
   p.locks = locks;
   p.status = status;
@@ -581,6 +608,30 @@ int chord_b200_indexed_rows(const void* x, const int32_t* packed, const void* sc
   return indexed_launch(x, packed, scale, sorted_ids, sorted_len, expert_ids, expert_len,
                         num_tokens_padded, nullptr, out_rows, locks, num_locks, workspace,
                         workspace_bytes, status, m, n, k, num_experts, top_k, block_m, stream);
+}
+
+int chord_b200_indexed_gate_up_silu(const void* x, const int32_t* packed, const void* scale,
+                                    const int32_t* sorted_ids, int64_t sorted_len,
+                                    const int32_t* expert_ids, int64_t expert_len,
+                                    const int32_t* num_tokens_padded, void* out, int32_t* locks,
+                                    int64_t num_locks, void* workspace, int64_t workspace_bytes,
+                                    int32_t* status, int64_t m, int64_t n, int64_t k,
+                                    int64_t num_experts, int64_t top_k, int64_t block_m, void* stream) {
+  CHORD_REQUIRE(out != nullptr, "null output pointer");
+  CHORD_REQUIRE(n > 0 && n % (2 * chord::kBlockN) == 0,
+                "fused gate_up needs N=%lld to be a multiple of 256 (gate rows, then as many up rows)",
+                static_cast<long long>(n));
+  return indexed_launch(x, packed, scale, sorted_ids, sorted_len, expert_ids, expert_len,
+                        num_tokens_padded, out, nullptr, locks, num_locks, workspace, workspace_bytes,
+                        status, m, n, k, num_experts, top_k, block_m, stream, /*fuse_silu=*/1);
+}
+
+int chord_b200_gate_up_silu_supported(int64_t n, int64_t k, int64_t block_m) {
+  if (n <= 0 || n % (2 * chord::kBlockN) != 0 || k <= 0 || k % 64 != 0 || block_m <= 0) return 0;
+  const int mma_n = chord::round_up16(block_m);
+  chord::OptionsReadLock options_guard(chord::options_mutex());
+  if (mma_n == 16) return chord::options().decode_kernel != 0 && k % chord::kDecStageK == 0;
+  return mma_n >= 64 && mma_n <= 128 && chord::options().pregather != 0;
 }
 
 int chord_b200_indexed_static_scratch(const void* x, const int32_t* packed, const void* scale,

@@ -76,7 +76,7 @@ __host__ __device__ inline uint32_t decode_stage_bytes(int mma_n) {
 __device__ __forceinline__ TileInfo decode_tile_small(const GemmParams& p, const int32_t* group_prefix,
                                                       int32_t tile) {
   TileInfo t;
-  const int32_t n_blocks = p.n / kBlockN;
+  const int32_t n_blocks = (p.n >> p.fuse_silu) / kBlockN;  // fused SiLU*mul: one tile per gate block
   const int32_t mb = tile / n_blocks;
   t.n0 = (tile - mb * n_blocks) * kBlockN;
   t.m0 = 0;
@@ -250,6 +250,115 @@ static __device__ __noinline__ void decode_drain(uint32_t d_addr, __nv_bfloat16*
   }
 }
 
+__device__ __forceinline__ float silu_f32(float v) { return v / (1.0f + __expf(-v)); }
+
+// decode_drain() for a gate_up tile with SiLU*mul fused in: the worker's accumulator holds
+// the gate block in columns 0-15 and the up block in columns 16-31 (16-token tiles); a
+// stream-K slice publishes or collects both, and the warp stores
+// bf16(silu(gate) * up) for its 32 rows of the block into a [rows, N/2] tensor (`ldn`).
+// `covered` bit b says whether the segment had any stage of block b: a one-stage slice
+// touches only one of the two accumulators, and the other then counts as zero.
+static __device__ __noinline__ void decode_drain_silu(uint32_t d_addr, __nv_bfloat16* out_tile,
+                                                      void* const* out_rows, int32_t col0, int32_t ldn,
+                                                      int32_t rows, uint32_t covered, int32_t seg_type,
+                                                      int32_t seg_peer, float* workspace, size_t ws_slot,
+                                                      int32_t worker_id, int32_t* locks, int32_t lock_spins,
+                                                      int32_t* status, __nv_bfloat16* stage,
+                                                      uint32_t bar_id, uint32_t wt, bool ok) {
+  const uint32_t lane = threadIdx.x & 31u;
+  const uint32_t q = (threadIdx.x >> 5) & 3u;
+  ptx::tc_fence_after();
+  const bool shared_tile = seg_type != kSegFull;
+  bool lock_ok = true;
+  if (shared_tile) {
+    if (ok && seg_type == kSegOwner && wt == 0) {
+      const int* lock = locks + worker_id;
+      lock_ok = false;
+      for (int32_t spin = 0; spin < lock_spins; ++spin) {
+        if (ptx::ld_acquire(lock) >= seg_peer) {
+          lock_ok = true;
+          break;
+        }
+        __nanosleep(64);
+      }
+      if (!lock_ok && status) atomicOr(status, kStatusLockTimeout);
+    }
+    ptx::named_bar_sync(bar_id, 128);  // lock observed
+  }
+  if (ok) {
+    float gate[16], up[16];
+    {
+      uint32_t v[16];
+      ptx::tmem_ld_32x32b_x16(d_addr, v);
+      ptx::tmem_wait_ld();
+#pragma unroll
+      for (int i = 0; i < 16; ++i) gate[i] = (covered & 1u) ? __uint_as_float(v[i]) : 0.0f;
+      ptx::tmem_ld_32x32b_x16(d_addr + 16, v);
+      ptx::tmem_wait_ld();
+#pragma unroll
+      for (int i = 0; i < 16; ++i) up[i] = (covered & 2u) ? __uint_as_float(v[i]) : 0.0f;
+    }
+    if (seg_type == kSegContrib) {
+      float* dst = workspace + worker_id * ws_slot + q * 32 + lane;
+#pragma unroll
+      for (int i = 0; i < 16; ++i) __stcg(dst + i * kBlockN, gate[i]);
+#pragma unroll
+      for (int i = 0; i < 16; ++i) __stcg(dst + (16 + i) * kBlockN, up[i]);
+    } else {
+      if (seg_type == kSegOwner) {
+        // partials are added in worker order (deterministic)
+        const float* part = workspace + (worker_id + 1) * ws_slot + q * 32 + lane;
+        for (int32_t peer = 1; peer <= seg_peer; ++peer, part += ws_slot) {
+          float pg[16], pu[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) pg[i] = __ldcg(part + i * kBlockN);
+#pragma unroll
+          for (int i = 0; i < 16; ++i) pu[i] = __ldcg(part + (16 + i) * kBlockN);
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            gate[i] += pg[i];
+            up[i] += pu[i];
+          }
+        }
+      }
+      // eight tokens at a time through shared memory, as in decode_drain()
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          stage[i * 32 + lane] = __float2bfloat16_rn(silu_f32(gate[8 * half + i]) * up[8 * half + i]);
+        }
+        __syncwarp();
+        const uint32_t tj = lane >> 2, pc = lane & 3;
+        const int32_t row = __shfl_sync(0xffffffffu, rows, 8 * half + static_cast<int32_t>(tj));
+        const uint4 val = *reinterpret_cast<const uint4*>(stage + tj * 32 + pc * 8);
+        if (row >= 0) {
+          if (out_rows != nullptr) {
+            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(
+                __ldg(reinterpret_cast<const unsigned long long*>(out_rows) + row));
+            if (dst != nullptr) *reinterpret_cast<uint4*>(dst + col0 + pc * 8) = val;
+          } else {
+            *reinterpret_cast<uint4*>(out_tile + static_cast<size_t>(row) * ldn + pc * 8) = val;
+          }
+        }
+        __syncwarp();
+      }
+    }
+    ptx::tc_fence_before();
+    if (seg_type == kSegContrib) __threadfence();
+  }
+  if (shared_tile) {
+    ptx::named_bar_sync(bar_id, 128);  // all four warps' partials are written / read
+    if (wt == 0) {
+      if (seg_type == kSegContrib) ptx::red_release_add(locks + seg_peer, 1);
+      else if (lock_ok) locks[worker_id] = 0;
+    }
+  }
+}
+
+// kFuse: gate_up with SiLU*mul in the epilogue (its own instantiation, so that the plain
+// kernel's loops carry none of it).
+template <bool kFuse>
 __global__ void __launch_bounds__(kDecThreads, 1)
 w4a16_decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_s,
                     const GemmParams p) {
@@ -269,7 +378,12 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
   // all lanes and keeps them in uniform registers.
   const uint32_t warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0);
   const uint32_t lane = threadIdx.x & 31;
-  const int32_t k_steps = (p.k + kDecStageK - 1) / kDecStageK;  // ring stages per tile
+  // With SiLU*mul fused into the epilogue a tile is a gate block and its up block (weight
+  // rows n0.. and N/2 + n0..): its ring stages alternate between the two (even stage = gate,
+  // odd = up, both of K block stage / 2), each block accumulates into its own 16 columns,
+  // and the epilogue combines them.  (Host side: only for 16-token tiles and K % 128 == 0.)
+  constexpr int32_t fuse = kFuse ? 1 : 0;
+  const int32_t k_steps = ((p.k + kDecStageK - 1) / kDecStageK) << fuse;  // ring stages per tile
   const bool k_tail_half = (p.k % kDecStageK) != 0;             // last stage: first K half only
 
   // Set-up is on the critical path of a small launch (a batch of one token is a
@@ -337,7 +451,7 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
 
   const uint32_t tmem_base = __shfl_sync(0xffffffffu, sh.tmem_base, 0);  // uniform, see `warp`
   const uint32_t abort_addr = ptx::smem_u32(&sh.abort_flag);  // raised by any wait that gives up
-  const int32_t tiles = __shfl_sync(0xffffffffu, sh.m_blocks, 0) * (p.n / kBlockN);
+  const int32_t tiles = __shfl_sync(0xffffffffu, sh.m_blocks, 0) * ((p.n >> fuse) / kBlockN);
   // warps 0-3 feed, warps 4-7 issue the MMAs, warps 8-23 are the four workers
   const uint32_t wk = warp < 8 ? (warp & 3u) : (warp - 8) >> 2;
   // Worker ids interleave the CTAs (worker w of CTA c is c + w * grid), so that a launch
@@ -394,7 +508,12 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
           w_more = false;
           break;
         }
-        if (first) {
+        if (fuse) {
+          // stage u of the tile: K block u / 2 of the gate (u even) or up (u odd) block
+          w_row = wsm.t.expert * (p.k / 16) + (wsm.kb >> 1) * (kDecStageK / 16);
+          s_row = wsm.t.expert * (p.k / 32) + (wsm.kb >> 1) * (kDecStageK / 32);
+          w_col = wsm.t.n0 + (wsm.kb & 1) * (p.n >> 1);
+        } else if (first) {
           w_row = wsm.t.expert * (p.k / 16) + wsm.kb * (kDecStageK / 16);
           s_row = wsm.t.expert * (p.k / 32) + wsm.kb * (kDecStageK / 32);
           w_col = wsm.t.n0;
@@ -432,6 +551,7 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
         }
         src = p.x + xsm.kb * kDecStageK + piece * 8;
       }
+      if (fuse) src = p.x + (xsm.kb >> 1) * kDecStageK + piece * 8;  // both blocks read the same K block
       ptx::mbar_wait_sticky(xempty0 + xcur.s * 8u, xcur.ph ^ 1u, abort_addr, bad);
       if (bad != 0) break;
       const uint32_t xs = ring + xcur.s * stage_bytes;
@@ -474,38 +594,53 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
     // a 64-wide step needs four: kept off the warps that dequantise.  A stage carries two
     // steps (one operand slot each); the activation half of the stage goes back to the
     // feeder with the second one.
+    // This warp's loop is the critical path of the kernel (measured: the workers' warps
+    // wait for free operand slots a fifth of their time while this loop takes as long per
+    // step as the whole step), and what it costs is a chain of dependent scalar
+    // instructions on a scheduler it shares with four dequantising warps: so the operand
+    // descriptor is formed once and advanced by additions, the four MMAs of a step are one
+    // statement, and nothing else is computed between the wait and the issue.
     const uint32_t d_tm = tmem_base + col0 + kDecDCol;
+    const uint32_t a_tm0 = tmem_base + col0;
+    const uint64_t xdesc_ring = ptx::smem_desc_k_sw128(ring);  // activation rows of stage 0, first K half
+    const uint32_t stage_units = stage_bytes >> 4, half_units = x_half_bytes >> 4;  // descriptor units: 16 bytes
     StageCursor cur, slot;
+    uint32_t cur_units = 0;  // cur.s * stage_units
     uint32_t bad = 0;
     while (bad == 0 && iter.next(seg)) {
       const TileInfo t = decode_tile_small(p, sh.group_prefix, seg.tile);
       if (!t.valid) continue;
       const uint32_t idesc = ptx::idesc_bf16_f32(kBlockN, static_cast<uint32_t>(t.mma_n));
       uint32_t acc = 0;
+      uint32_t started = 0;  // fused SiLU*mul: bit b = block b's accumulator holds a sum already
       for (int32_t kb = seg.kb; bad == 0 && kb < seg.ke; ++kb) {
         // No wait is needed for the accumulator: the first store of a segment follows
         // its warp's share of the previous segment's epilogue.
         const int32_t halves = (k_tail_half && kb == k_steps - 1) ? 1 : 2;
-        const uint32_t stage = ring + cur.s * stage_bytes;
+        uint32_t d_blk = d_tm;
+        if (fuse) {
+          const uint32_t blk = static_cast<uint32_t>(kb) & 1u;
+          d_blk = d_tm + blk * 16u;
+          acc = (started >> blk) & 1u;
+          started |= 1u << blk;
+        }
+        uint64_t xdesc = xdesc_ring + cur_units;
         for (int32_t h = 0; h < halves; ++h) {
           ptx::mbar_wait_sticky(afull0 + slot.s * 8u, slot.ph, abort_addr, bad);
           if (h == 0) ptx::mbar_wait_sticky(xfull0 + cur.s * 8u, cur.ph, abort_addr, bad);
           ptx::tc_fence_after();
           if (lane == 0 && bad == 0) {
-            const uint64_t xdesc = ptx::smem_desc_k_sw128(stage + static_cast<uint32_t>(h) * x_half_bytes);
-            const uint32_t a_tm = tmem_base + col0 + slot.s * 32u;
-            ptx::mma_ts(d_tm, a_tm, xdesc, idesc, acc);
-            ptx::mma_ts(d_tm, a_tm + 8, xdesc + 2, idesc, 1);
-            ptx::mma_ts(d_tm, a_tm + 16, xdesc + 4, idesc, 1);
-            ptx::mma_ts(d_tm, a_tm + 24, xdesc + 6, idesc, 1);
+            ptx::mma_ts_k64(d_blk, a_tm0 + slot.s * 32u, xdesc, idesc, acc);
             if (h == halves - 1) ptx::mma_commit(xempty0 + cur.s * 8u);
             ptx::mma_commit(afree0 + slot.s * 8u);
           }
           __syncwarp();
           acc = 1;
+          xdesc += half_units;
           slot.advance(kDecSlots);
         }
         cur.advance(stages);
+        cur_units = cur.s == 0 ? 0u : cur_units + stage_units;
       }
     }
     if (bad != 0 && lane == 0 && p.status) atomicOr(p.status, kStatusMmaTimeout);
@@ -533,9 +668,18 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
     const uint32_t ring_bytes = stages * stage_bytes;
     uint32_t stage_off = 0, stage_bar = 0, stage_ph = 0, slot_bar = 0, slot_ph = 0;
     uint32_t bad = 0;  // sticky: set by the first bounded wait that gives up
-    const size_t ws_slot = static_cast<size_t>(kBlockN) * p.mma_n;
+    const size_t ws_slot = (static_cast<size_t>(kBlockN) * p.mma_n) << fuse;
 
     auto drain = [&](const Segment& sg, int32_t rows, int32_t n0, uint32_t dcol, int32_t mma_n) {
+      if (fuse) {
+        // blocks the segment's stages touched: even stages are the gate block, odd ones the up block
+        const uint32_t covered = (sg.ke - sg.kb >= 2) ? 3u : (1u << (sg.kb & 1));
+        decode_drain_silu(tmem_base + ((q * 32u) << 16) + dcol, p.out + n0 + q * 32, p.out_row_ptr,
+                          n0 + static_cast<int32_t>(q) * 32, p.n >> 1, rows, covered, sg.type, sg.peer,
+                          p.workspace, ws_slot, worker_id, p.locks, p.lock_spins, p.status,
+                          &ws.stage[q][0][0], bar_id, wt, bad == 0);
+        return;
+      }
       decode_drain(tmem_base + ((q * 32u) << 16) + dcol, p.out + n0 + q * 32, p.out_row_ptr,
                    n0 + static_cast<int32_t>(q) * 32, p.n, rows, mma_n, sg.type,
                    sg.peer, p.workspace, ws_slot, worker_id, p.locks, p.lock_spins, p.status,

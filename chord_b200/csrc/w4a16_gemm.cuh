@@ -124,6 +124,7 @@ struct GemmParams {
   int32_t x_stages;     // depth of the activation ring
   int32_t issuers;      // 1, 2 or 4 MMA issuers (and accumulators)
   int32_t ksplit;       // single-issuer layouts: a second issuer takes the second K half of tiles of <= 128 tokens
+  int32_t fuse_silu;    // 1 = gate_up with SiLU*mul in the epilogue: a tile is gate block j and up block j (row N/2 + 128 j), out is [rows, N/2]
   int32_t npair;        // 1 = a tile is two neighbouring 128-row weight blocks sharing one activation stage (tiles of <= 128 tokens)
   int32_t a_stages;     // depth of the TMEM A ring; accumulators start at column 64 * a_stages
   int32_t num_locks;
@@ -265,9 +266,10 @@ __device__ __forceinline__ TileInfo decode_tile(const GemmParams& p, const GemmS
                                                 int32_t tile) {
   TileInfo t;
   // With `npair` a tile spans two neighbouring 128-row weight blocks (n0 and n0 + 128).
-  const int32_t n_blocks = p.n / (kBlockN << p.npair);
+  // With fused SiLU*mul the two blocks are gate block n0 and up block N/2 + n0.
+  const int32_t n_blocks = p.fuse_silu ? (p.n >> 1) / kBlockN : p.n / (kBlockN << p.npair);
   const int32_t mb = tile / n_blocks;
-  t.n0 = (tile - mb * n_blocks) * (kBlockN << p.npair);
+  t.n0 = (tile - mb * n_blocks) * (p.fuse_silu ? kBlockN : (kBlockN << p.npair));
   t.m0 = 0;
   t.limit = 0;
   t.mma_n = p.mma_n;
@@ -597,7 +599,8 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
 
   const uint32_t tmem_base = __shfl_sync(0xffffffffu, sh.tmem_base, 0);  // uniform, see `warp`
   volatile uint32_t* abort_flag = &sh.abort_flag;
-  const int32_t tiles = __shfl_sync(0xffffffffu, sh.m_blocks, 0) * (p.n / (kBlockN << p.npair));
+  const int32_t tiles = __shfl_sync(0xffffffffu, sh.m_blocks, 0) *
+                        (p.fuse_silu ? (p.n >> 1) / kBlockN : p.n / (kBlockN << p.npair));
   SegmentIterator iter;
   iter.init(tiles, k_iters, static_cast<int32_t>(gridDim.x), static_cast<int32_t>(blockIdx.x));
   Segment seg;
@@ -617,7 +620,9 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
         const TileInfo t = decode_tile(p, sh, seg.tile);
         if (!t.valid) continue;
         const int32_t col = weights ? 2 * t.n0 : t.n0;
-        const int32_t col_step = weights ? 2 * kBlockN : kBlockN;  // to the tile's second weight block
+        // to the tile's second weight block: the next 128 rows, or the up rows of a fused gate_up
+        const int32_t block_step = p.fuse_silu ? (p.n >> 1) : kBlockN;
+        const int32_t col_step = weights ? 2 * block_step : block_step;
         int32_t row = t.expert * rows_per_expert + seg.kb * rows_per_stage;
         for (int32_t kb = seg.kb; ok && kb < seg.ke; ++kb) {
           for (int32_t sub = 0; sub < w_per_kb; ++sub) {
@@ -1180,7 +1185,11 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
       // in this segment only if one of them falls inside it.  (With `npair` accumulator
       // `sub` is the tile's weight block `sub` instead, and nothing is summed.)
       const uint32_t seg_len = static_cast<uint32_t>(seg.ke - seg.kb);
-      for (int32_t sub = 0; sub < w_per_kb; ++sub) {
+      // Fused SiLU*mul: one pass, which reads both accumulators (gate, up), combines them
+      // and writes a [rows, N/2] tensor.
+      const bool fuse = p.fuse_silu != 0;
+      const int32_t ldn = fuse ? (p.n >> 1) : p.n;
+      for (int32_t sub = 0; sub < (fuse ? 1 : w_per_kb); ++sub) {
       const int32_t n_sub = t.n0 + sub * kBlockN + static_cast<int32_t>(q) * 32;
       __nv_bfloat16* out_tile = p.out + n_sub;
       const size_t ws_sub = static_cast<size_t>(sub) * ws_block;
@@ -1208,10 +1217,26 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
 #pragma unroll
           for (int j = 0; j < 16; ++j) acc[j] += __uint_as_float(v[j]);
         }
+        float up[16];
+        if (fuse) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) up[j] = 0.0f;
+          if (computed) {
+            uint32_t v[16];
+            ptx::tmem_ld_32x32b_x16(d_addr + d_cols + c0, v);
+            ptx::tmem_wait_ld();
+#pragma unroll
+            for (int j = 0; j < 16; ++j) up[j] = __uint_as_float(v[j]);
+          }
+        }
         if (seg.type == kSegContrib) {
           float* dst = p.workspace + blockIdx.x * ws_slot + ws_sub + static_cast<size_t>(c0) * kBlockN + et;
 #pragma unroll
           for (int j = 0; j < 16; ++j) __stcg(dst + j * kBlockN, acc[j]);
+          if (fuse) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) __stcg(dst + ws_block + j * kBlockN, up[j]);
+          }
           continue;
         }
         if (seg.type == kSegOwner && computed) {
@@ -1220,7 +1245,15 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
                                static_cast<size_t>(c0) * kBlockN + et;
 #pragma unroll
             for (int j = 0; j < 16; ++j) acc[j] += __ldcg(src + j * kBlockN);
+            if (fuse) {
+#pragma unroll
+              for (int j = 0; j < 16; ++j) up[j] += __ldcg(src + ws_block + j * kBlockN);
+            }
           }
+        }
+        if (fuse) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) acc[j] = acc[j] / (1.0f + __expf(-acc[j])) * up[j];
         }
         // Transpose through shared memory so that global stores are 16 bytes wide: the
         // warp holds 32 weight rows x 16 tokens (one token per register); staged as
@@ -1242,7 +1275,7 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
                   __ldg(reinterpret_cast<const unsigned long long*>(p.out_row_ptr) + row));
               if (dst != nullptr) *reinterpret_cast<uint4*>(dst + n_sub + piece * 8) = v;
             } else {
-              *reinterpret_cast<uint4*>(out_tile + static_cast<size_t>(row) * p.n + piece * 8) = v;
+              *reinterpret_cast<uint4*>(out_tile + static_cast<size_t>(row) * ldn + piece * 8) = v;
             }
           }
         }

@@ -299,7 +299,6 @@ class ExpertParallelLayer:
         self.recv_count = torch.zeros(1, dtype=torch.int32, device=dev)
         self.send_pos = torch.empty(lay.routed_rows, dtype=torch.int32, device=dev)
         self.row_ptr = torch.zeros(lay.capacity, dtype=torch.int64, device=dev)
-        self.gate_up = torch.empty((lay.capacity, self.inter2), dtype=torch.bfloat16, device=dev)
         self.hidden = torch.empty((lay.capacity, self.inter2 // 2), dtype=torch.bfloat16, device=dev)
 
     # -- helpers ---------------------------------------------------------------------
@@ -361,8 +360,7 @@ class ExpertParallelLayer:
 
     def local_experts(self) -> None:
         from . import _lib
-        from .fused_ops import silu_mul
-        from .indexed_gemm import gemm_scratch, indexed, status_word
+        from .indexed_gemm import gemm_scratch, indexed_gate_up_silu, status_word
 
         lay = self.layout
         span = self._span("align")
@@ -375,10 +373,8 @@ class ExpertParallelLayer:
         self._end(span)
         span = self._span("experts")
         routing = (self.sorted_ids, self.expert_ids, self.padded)
-        indexed(self.recv_x, self.w13, *routing, 1, locks=self.locks, outputs=self.gate_up,
-                block_m=self.block_m)
-        silu_mul(self.gate_up, sorted_ids=self.sorted_ids, num_tokens_padded=self.padded,
-                 outputs=self.hidden)
+        indexed_gate_up_silu(self.recv_x, self.w13, *routing, 1, locks=self.locks, outputs=self.hidden,
+                             block_m=self.block_m)
         # down: every result row goes straight to the result tensor of the rank it came from
         locks, workspace, ws_bytes = gemm_scratch(self.device, self.block_m, self.locks,
                                                   self.sorted_ids.numel(), self.w2.k)
@@ -403,15 +399,14 @@ class ExpertParallelLayer:
         return self.routed[: self._routes].view(-1, self.top_k, self.hidden_out)
 
     def _single_rank(self, x, topk_ids):
-        from .fused_ops import moe_align_block_size, silu_mul
-        from .indexed_gemm import indexed, select_block_m
+        from .fused_ops import moe_align_block_size
+        from .indexed_gemm import indexed, indexed_gate_up_silu, select_block_m
 
         span = self._span("experts")
         tokens = x.size(0)
         block_m = select_block_m(self.w13.n, self.w13.k, self.experts_per_rank, tokens * self.top_k)
         routing = moe_align_block_size(topk_ids, block_m, self.experts_per_rank)
-        gate_up = indexed(x, self.w13, *routing, self.top_k, locks=self.locks, block_m=block_m)
-        hidden = silu_mul(gate_up, sorted_ids=routing[0], num_tokens_padded=routing[2])
+        hidden = indexed_gate_up_silu(x, self.w13, *routing, self.top_k, locks=self.locks, block_m=block_m)
         out = indexed(hidden, self.w2, *routing, 1, locks=self.locks, block_m=block_m)
         self._end(span)
         return out.view(tokens, self.top_k, self.hidden_out)

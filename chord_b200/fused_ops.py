@@ -32,7 +32,7 @@ def silu_mul(gate_up: torch.Tensor, *, sorted_ids: torch.Tensor | None = None,
           or not outputs.is_contiguous() or outputs.device != device):
         raise ValueError(f"outputs must be contiguous BF16 {(rows, inter)} on {device}")
     lib = _lib.load()
-    with torch.cuda.device(device):
+    with _lib.on_device(device):
         stream = _lib.stream_handle(device)
         if sorted_ids is None:
             _lib.check(lib.chord_b200_silu_mul(gate_up.data_ptr(), outputs.data_ptr(), rows, inter, stream))
@@ -68,7 +68,7 @@ def moe_align_block_size(topk_ids: torch.Tensor, block_m: int, num_experts: int,
     expert_ids = torch.empty(blocks, dtype=torch.int32, device=device)
     num_tokens_padded = torch.empty(1, dtype=torch.int32, device=device)
     lib = _lib.load()
-    with torch.cuda.device(device):
+    with _lib.on_device(device):
         _lib.check(lib.chord_b200_moe_align_block_size(
             topk_ids.data_ptr(), numel, expert_base, num_experts, block_m,
             sorted_ids.data_ptr(), sorted_ids.numel(), expert_ids.data_ptr(), expert_ids.numel(),

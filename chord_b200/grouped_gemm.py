@@ -74,7 +74,7 @@ def w4a16_masked(
         _checks.bf16_output(outputs, (groups * max_m, weight.n), device, exact_shape=False)
     tile_m = masked_tile_m(expected_m)
     lib = _lib.load()
-    with torch.cuda.device(device):
+    with _lib.on_device(device):
         locks, workspace, ws_bytes = gemm_scratch(device, tile_m, None)
         _lib.check(lib.chord_b200_masked(
             grouped.data_ptr(), weight.packed.data_ptr(), weight.scale.data_ptr(),
@@ -115,7 +115,7 @@ def w4a16_contiguous(
     else:
         _checks.bf16_output(outputs, (m, weight.n), device, exact_shape=False)
     lib = _lib.load()
-    with torch.cuda.device(device):
+    with _lib.on_device(device):
         locks, workspace, ws_bytes = gemm_scratch(device, 256, None)
         _lib.check(lib.chord_b200_contiguous(
             inputs.data_ptr(), weight.packed.data_ptr(), weight.scale.data_ptr(),

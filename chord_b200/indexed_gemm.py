@@ -4,6 +4,8 @@ chord_kernels/operator/api.py:300-409, on the sm_100a tcgen05 kernel."""
 
 from __future__ import annotations
 
+import functools
+
 import torch
 
 from . import _checks, _lib
@@ -80,22 +82,32 @@ def gemm_scratch(device: torch.device, tile_tokens: int, locks: torch.Tensor | N
     and, for `indexed` with large routing blocks, the slot-ordered copy of the routed
     rows) comes from torch's caching allocator on every call, as in the reference's
     launcher (csrc/launcher/launcher.cpp:110-123): stream-ordered and graph-pool safe."""
-    lib = _lib.load()
-    need_words = lib.chord_b200_gemm_lock_words()
+    need_words, ws_bytes = _scratch_sizes(_device_index(device), tile_tokens, sorted_len, k,
+                                          _lib.options_epoch())
     if locks is None:
         locks = default_locks(device)
     elif locks.numel() < need_words:
         raise RuntimeError(
             f"locks has {locks.numel()} lock words, this launch needs at least {need_words}"
         )
+    workspace = torch.empty(ws_bytes // 4, dtype=torch.float32, device=device)
+    return locks, workspace, ws_bytes
+
+
+@functools.lru_cache(maxsize=256)
+def _scratch_sizes(device_index: int, tile_tokens: int, sorted_len: int, k: int, options_epoch: int):
+    """(lock words, workspace bytes) of a launch, asked of the library once per shape,
+    device and option setting (the current device must be ``device_index``)."""
+    del device_index, options_epoch  # cache keys only
+    lib = _lib.load()
+    need_words = lib.chord_b200_gemm_lock_words()
     if sorted_len > 0:
         ws_bytes = lib.chord_b200_indexed_workspace_bytes(tile_tokens, sorted_len, k)
     else:
         ws_bytes = lib.chord_b200_gemm_workspace_bytes(tile_tokens)
-    if ws_bytes < 0:
+    if need_words < 0 or ws_bytes < 0:
         raise ValueError(_lib.last_error())
-    workspace = torch.empty(ws_bytes // 4, dtype=torch.float32, device=device)
-    return locks, workspace, ws_bytes
+    return need_words, ws_bytes
 
 
 def select_block_m(shape_n: int, shape_k: int, num_experts: int, routed_m: int) -> int:
@@ -178,7 +190,7 @@ def w4a16_indexed(
                                  num_experts)
 
     lib = _lib.load()
-    with torch.cuda.device(device):
+    with _lib.on_device(device):
         locks, workspace, ws_bytes = gemm_scratch(device, block_m, locks, sorted_ids.numel(), shape_k)
         _lib.check(lib.chord_b200_indexed(
             inputs.data_ptr(), packed.data_ptr(), scale.data_ptr(),
@@ -187,6 +199,83 @@ def w4a16_indexed(
             locks.data_ptr(), locks.numel(), workspace.data_ptr(), ws_bytes,
             status_word(device).data_ptr(),
             inputs.size(0), shape_n, shape_k, num_experts, top_k, block_m,
+            _lib.stream_handle(device),
+        ))
+    return outputs
+
+
+def indexed_gate_up_silu(
+    activation: torch.Tensor,
+    weight: PreparedWeight,
+    sorted_ids: torch.Tensor,
+    expert_ids: torch.Tensor,
+    num_tokens_padded: torch.Tensor,
+    top_k: int,
+    *,
+    locks: torch.Tensor | None = None,
+    outputs: torch.Tensor | None = None,
+    block_m: int | None = None,
+) -> torch.Tensor:
+    """The gate_up projection with SiLU*mul applied in the GEMM's epilogue.
+
+    ``weight`` is the fused w13 weight (``N`` rows: gate rows, then as many up rows).
+    Returns BF16 ``[M * top_k, N / 2]`` with ``silu(gate) * up`` for every routed row,
+    computed from the FP32 accumulators; rows no routed id names are left untouched.
+    Arguments as for :func:`indexed`.  Where the fused kernel does not apply (routing
+    blocks of 17 to 63 rows, or more than 128) the same result is produced by
+    ``indexed`` followed by ``silu_mul`` (there rounded to BF16 in between).
+    No counterpart in the reference, which leaves the activation to its caller.
+    """
+    from .fused_ops import silu_mul
+
+    if not isinstance(activation, torch.Tensor) or activation.ndim != 2 or activation.dtype != torch.bfloat16:
+        raise TypeError("inputs must be a 2D torch.bfloat16 tensor")
+    _checks.tensor("inputs", activation, nonempty=True)
+    device = activation.device
+    _checks.supported_gpu(device)
+    packed, scale, num_experts, shape_n, shape_k = _checks.prepared_weight(weight, device)
+    if shape_n % 256:
+        raise ValueError(f"a fused gate/up weight needs N divisible by 256, got {shape_n}")
+    if activation.size(1) != shape_k:
+        raise ValueError(f"inputs K={activation.size(1)} does not match the weight's K={shape_k}")
+    _checks.integer("top_k", top_k, minimum=1)
+    routed_m = activation.size(0) * top_k
+    block_m = (select_block_m(shape_n, shape_k, num_experts, routed_m) if block_m is None
+               else _checks.routing_block_m(block_m, MAX_BLOCK_M))
+    inter = shape_n // 2
+    if outputs is None:
+        outputs = torch.empty((routed_m, inter), dtype=torch.bfloat16, device=device)
+    else:
+        _checks.bf16_output(outputs, (routed_m, inter), device, exact_shape=True)
+    lib = _lib.load()
+    if not lib.chord_b200_gate_up_silu_supported(shape_n, shape_k, block_m):
+        gate_up = w4a16_indexed(activation, weight, sorted_ids, expert_ids, num_tokens_padded, top_k,
+                                locks=locks, block_m=block_m)
+        return silu_mul(gate_up, sorted_ids=sorted_ids, num_tokens_padded=num_tokens_padded,
+                        outputs=outputs)
+    _checks.tensor("sorted_ids", sorted_ids, dtype=torch.int32, ndim=1, device=device)
+    _checks.tensor("expert_ids", expert_ids, dtype=torch.int32, ndim=1, device=device)
+    _checks.tensor("num_tokens_padded", num_tokens_padded, dtype=torch.int32, device=device)
+    if locks is not None:
+        _checks.tensor("locks", locks, dtype=torch.int32, ndim=1, device=device)
+    with _lib.on_device(device):
+        need_words = lib.chord_b200_gemm_lock_words()
+        if locks is None:
+            locks = default_locks(device)
+        elif locks.numel() < need_words:
+            raise RuntimeError(
+                f"locks has {locks.numel()} lock words, this launch needs at least {need_words}")
+        ws_bytes = lib.chord_b200_gate_up_silu_workspace_bytes(block_m, sorted_ids.numel(), shape_k)
+        if ws_bytes < 0:
+            raise ValueError(_lib.last_error())
+        workspace = torch.empty(ws_bytes // 4, dtype=torch.float32, device=device)
+        _lib.check(lib.chord_b200_indexed_gate_up_silu(
+            activation.data_ptr(), packed.data_ptr(), scale.data_ptr(),
+            sorted_ids.data_ptr(), sorted_ids.numel(), expert_ids.data_ptr(), expert_ids.numel(),
+            num_tokens_padded.data_ptr(), outputs.data_ptr(),
+            locks.data_ptr(), locks.numel(), workspace.data_ptr(), ws_bytes,
+            status_word(device).data_ptr(),
+            activation.size(0), shape_n, shape_k, num_experts, top_k, block_m,
             _lib.stream_handle(device),
         ))
     return outputs
@@ -224,4 +313,4 @@ def indexed(
     )
 
 
-__all__ = ["check_status", "indexed", "indexed_block_m", "w4a16_indexed", "select_block_m", "status_word"]
+__all__ = ["check_status", "indexed", "indexed_gate_up_silu", "indexed_block_m", "w4a16_indexed", "select_block_m", "status_word"]

@@ -148,6 +148,29 @@ int chord_b200_indexed(const void* x, const int32_t* packed, const void* scale,
                        int32_t* status, int64_t m, int64_t n, int64_t k, int64_t num_experts,
                        int64_t top_k, int64_t block_m, void* stream);
 
+/* ---- gate_up GEMM with SiLU*mul in the epilogue -----------------------------------
+ * No counterpart in the reference, which stops at the GEMM and leaves the activation to
+ * its caller (docs/getting_started.md:5-14).  Same arguments as chord_b200_indexed for
+ * a fused gate/up weight of N rows (gate rows first, then as many up rows: the w13
+ * convention of tests/generators.py:419-420), but
+ *   out[id, j] = bf16(silu(g) * u),  g = x[id / top_k] . W[e][j],  u = x[id / top_k] . W[e][N/2 + j]
+ * with g and u taken from the FP32 accumulators, for j < N/2: out is bf16
+ * [m * top_k, N/2] and the [m * top_k, N] intermediate never exists.  Each tile
+ * computes a 128-row gate block and its up block side by side.
+ * Available (chord_b200_gate_up_silu_supported() != 0) for routing blocks of at most 16
+ * rows when K % 128 == 0, and for blocks of 64 to 128 rows; N % 256 == 0.  Otherwise
+ * the call returns 1 and the caller runs chord_b200_indexed + chord_b200_silu_mul.
+ * workspace: chord_b200_gate_up_silu_workspace_bytes(block_m, sorted_len, k). */
+int chord_b200_indexed_gate_up_silu(const void* x, const int32_t* packed, const void* scale,
+                                    const int32_t* sorted_ids, int64_t sorted_len,
+                                    const int32_t* expert_ids, int64_t expert_len,
+                                    const int32_t* num_tokens_padded, void* out, int32_t* locks,
+                                    int64_t num_locks, void* workspace, int64_t workspace_bytes,
+                                    int32_t* status, int64_t m, int64_t n, int64_t k,
+                                    int64_t num_experts, int64_t top_k, int64_t block_m, void* stream);
+int chord_b200_gate_up_silu_supported(int64_t n, int64_t k, int64_t block_m);
+int64_t chord_b200_gate_up_silu_workspace_bytes(int64_t block_m, int64_t sorted_len, int64_t k);
+
 /* ---- indexed GEMM with a table of output row addresses ----------------------------
  * No counterpart in the reference, whose epilogue stores row `id` at out + id * n
  * (include/humming/epilogue/gmem_writer.cuh:93-103).  Same operation and arguments as

@@ -103,3 +103,21 @@ def test_single_rank_layer_needs_no_process_group():
     out = ep.moe_layer(x, topk, 2, lambda rows, ids: rows * (ids.view(-1, 1).float() + 1))
     want = x.repeat_interleave(2, 0) * (topk.reshape(-1, 1).float() + 1)
     assert torch.equal(out, want.view(4, 2, 3))
+
+
+def test_exchange_layout_covers_the_worst_case():
+    """Buffer layout of the peer-memory exchange: the receive buffers hold every route of
+    every rank (the worst case: all of them land on one rank), regions are 256-byte
+    aligned and do not overlap."""
+    from chord_b200.ep import ExchangeLayout
+
+    lay = ExchangeLayout.build(world=8, max_tokens=512, top_k=8, hidden_in=7168, hidden_out=7168,
+                               state_bytes=17160)
+    assert lay.routed_rows == 4096 and lay.capacity == 8 * 4096
+    regions = [(lay.state, 17160), (lay.recv_tag, 2 * lay.capacity * 4),
+               (lay.recv_x, lay.capacity * 7168 * 2), (lay.routed, lay.routed_rows * 7168 * 2)]
+    end = 0
+    for start, size in regions:
+        assert start % 256 == 0 and start >= end
+        end = start + size
+    assert lay.total >= end

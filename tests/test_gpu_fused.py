@@ -128,3 +128,40 @@ def test_peer_memory_exchange_with_all_ranks_on_one_gpu(device, world, tokens, t
             assert O.cosine_diff(got, ref) <= 5e-3
             assert O.max_abs_rel(got, ref) <= 2e-2   # two GEMMs and an activation, each rounded to BF16
         xs = [x * 0.5 for x in xs]               # new inputs for the second call
+
+
+@pytest.mark.parametrize("experts,n,k,m,top_k,block_m", [
+    (8, 512, 512, 24, 2, 16),       # decode kernel: gate and up block side by side in one worker
+    (2, 256, 7168, 6, 1, 16),       # few tiles on many workers: every tile through the stream-K fix-up
+    (6, 1024, 640, 300, 2, 128),    # general kernel, 128-row routing blocks (slot-ordered copy of the rows)
+    (4, 512, 384, 200, 1, 64),      # general kernel, 64-row blocks
+    (4, 512, 256, 40, 2, 32),       # no fused kernel for this block size: GEMM + SiLU*mul behind the same call
+])
+def test_gate_up_with_fused_silu_mul(device, experts, n, k, m, top_k, block_m):
+    """`indexed_gate_up_silu` against the oracle's gate_up -> SiLU*mul: the fused kernels
+    apply the activation to the FP32 accumulators (one rounding), so the comparison is
+    against silu(gate) * up of the oracle's FP32 GEMM result."""
+    import chord_b200
+    from tests.cases import make_indexed_case
+
+    case = make_indexed_case(num_experts=experts, n=n, k=k, m=m, top_k=top_k, block_m=block_m, seed=70 + m)
+    w = chord_b200.pack_w4a16(case["codes"].to(device), case["scale"].to(device))
+    routing = (case["sorted_ids"].to(device), case["expert_ids"].to(device),
+               case["num_tokens_padded"].to(device).reshape(1))
+    locks = torch.zeros(1024, dtype=torch.int32, device=device)
+    out = torch.full((m * top_k, n // 2), float("nan"), dtype=torch.bfloat16, device=device)
+    outs = []
+    for _ in range(3):
+        res = chord_b200.indexed_gate_up_silu(case["x"].to(device), w, *routing, top_k, locks=locks,
+                                              outputs=out, block_m=block_m)
+        outs.append(res.clone())
+    chord_b200.check_status(device)
+    assert bool((locks == 0).all())
+    ref = O.reference_indexed(case["x"], case["codes"], case["scale"], case["topk_ids"], top_k)
+    want = torch.nn.functional.silu(ref[:, : n // 2]) * ref[:, n // 2:]
+    got = outs[0].float().cpu()
+    assert not bool(torch.isnan(got).any())      # every route of this case is local
+    assert O.cosine_diff(got, want) <= 5e-3
+    assert O.max_abs_rel(got, want) <= 1.5e-2    # BF16 output of a product of two GEMM results
+    for other in outs[1:]:
+        assert torch.equal(other.view(torch.int16), outs[0].view(torch.int16))

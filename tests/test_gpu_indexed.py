@@ -370,3 +370,36 @@ def test_lock_wait_gives_up_and_reports(device):
     assert int(status_word(device).item()) == 0      # check_status clears the word
     good, _ = run_case(device, case)                  # fresh locks: correct again
     check_against_oracle(good, case)
+
+
+def test_programmatic_dependent_launch_gives_the_same_bits(device):
+    """gate_up -> SiLU*mul -> down with option pdl = 1 (each launch may become resident
+    while its predecessor drains and synchronises with it through griddepcontrol.wait;
+    the reference sets the same launch attribute for enable_pdl,
+    csrc/launcher/launcher.cpp:440-451): bit-equal to the plain launches, repeatedly."""
+    import chord_b200
+    from chord_b200 import _lib
+
+    case = make_indexed_case(num_experts=8, n=1024, k=512, m=64, top_k=2, block_m=16, seed=51)
+    codes2, scale2 = make_checkpoint_weights(8, 512, 512, seed=52)
+    w13 = chord_b200.pack_w4a16(case["codes"].to(device), case["scale"].to(device))
+    w2 = chord_b200.pack_w4a16(codes2.to(device), scale2.to(device), packed=True)
+    routing = (case["sorted_ids"].to(device), case["expert_ids"].to(device),
+               case["num_tokens_padded"].to(device).reshape(1))
+    locks = torch.zeros(1024, dtype=torch.int32, device=device)
+    x = case["x"].to(device)
+
+    def step():
+        gate_up = chord_b200.indexed(x, w13, *routing, 2, locks=locks, block_m=16)
+        hidden = chord_b200.silu_mul(gate_up, sorted_ids=routing[0], num_tokens_padded=routing[2])
+        return chord_b200.indexed(hidden, w2, *routing, 1, locks=locks, block_m=16)
+
+    plain = step().clone()
+    _lib.set_option("pdl", 1)
+    try:
+        for _ in range(5):
+            assert torch.equal(step().view(torch.int16), plain.view(torch.int16))
+    finally:
+        _lib.set_option("pdl", 0)
+    chord_b200.check_status(device)
+    assert bool((locks == 0).all())

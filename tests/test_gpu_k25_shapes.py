@@ -73,6 +73,10 @@ def test_decode_step_at_the_benchmarked_configuration(device, k25, batch):
     chord_b200.indexed(x.to(device), w13, *routing, TOP_K, locks=locks, outputs=gate_up, block_m=block_m)
     chord_b200.silu_mul(gate_up, sorted_ids=routing[0], num_tokens_padded=routing[2], outputs=hidden)
     chord_b200.indexed(hidden, w2, *routing, 1, locks=locks, outputs=out, block_m=block_m)
+    # the benchmark's step takes gate_up and SiLU*mul in one launch
+    fused = torch.full((routes, INTER), float("nan"), dtype=torch.bfloat16, device=device)
+    chord_b200.indexed_gate_up_silu(x.to(device), w13, *routing, TOP_K, locks=locks, outputs=fused,
+                                    block_m=block_m)
     torch.cuda.synchronize()
     assert int(status_word(device).item()) == 0
     assert bool((locks == 0).all())
@@ -99,6 +103,12 @@ def test_decode_step_at_the_benchmarked_configuration(device, k25, batch):
         # SiLU*mul on the kernel's gate_up (fast exponential on the device: one BF16 step)
         want = O.silu_mul(gate_up[rows.to(device)].cpu()).float()
         assert (hidden_c[rows].float() - want).abs().max() <= 2.0 ** -7 * want.abs().max()
+        # fused launch: the activation of the FP32 gate_up result, rounded once
+        act = torch.nn.functional.silu(ref13[:, :INTER]) * ref13[:, INTER:]
+        fused_rows = fused[rows.to(device)].float().cpu()
+        assert O.cosine_diff(fused_rows, act) <= COS_INDEXED
+        assert O.max_abs_rel(fused_rows, act) <= 1.5e-2
+    assert torch.equal(~torch.isnan(fused.float().cpu()).any(dim=1), local)
 
 
 @pytest.mark.parametrize("projection", ["gate_up", "down"])
