@@ -367,7 +367,15 @@ int launch_gemm(GemmParams p, const void* x, const int32_t* packed, const void* 
   const int turn = groups > p.issuers ? groups : p.issuers;  // both are powers of two
   p.a_stages -= p.a_stages % turn;
   p.w_stages -= p.w_stages % groups;
-  p.x_stages -= p.x_stages % p.issuers;
+  if (p.npair) {
+    // both issuers consume every activation stage (nobody takes turns on that ring), and
+    // with two weight stages per activation stage a deeper activation ring is affordable
+    p.x_stages = p.mma_n <= 64 ? 6 : 4;
+    p.w_stages = pick_w_stages(dev, p.mma_n, p.x_stages);
+    p.w_stages -= p.w_stages % groups;
+  } else {
+    p.x_stages -= p.x_stages % p.issuers;
+  }
   CHORD_REQUIRE(p.a_stages >= turn && p.w_stages >= groups && p.x_stages >= p.issuers,
                 "internal: ring depths %d/%d/%d too small for %d groups and %d issuers",
                 p.a_stages, p.w_stages, p.x_stages, groups, p.issuers);

@@ -629,7 +629,7 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
           ptx::mbar_wait_sticky(afull0 + slot.s * 8u, slot.ph, abort_addr, bad);
           if (h == 0) ptx::mbar_wait_sticky(xfull0 + cur.s * 8u, cur.ph, abort_addr, bad);
           ptx::tc_fence_after();
-          if (lane == 0 && bad == 0) {
+          if (bad == 0 && ptx::elect_one()) {  // (elected, not `lane == 0`: measured 1.5 % faster)
             ptx::mma_ts_k64(d_blk, a_tm0 + slot.s * 32u, xdesc, idesc, acc);
             if (h == halves - 1) ptx::mma_commit(xempty0 + cur.s * 8u);
             ptx::mma_commit(afree0 + slot.s * 8u);
