@@ -103,6 +103,7 @@ def _apply_env_options(lib: ctypes.CDLL) -> None:
         ("CHORD_B200_DECODE_KERNEL", "decode_kernel"),
         ("CHORD_B200_PDL", "pdl"),
         ("CHORD_B200_NPAIR", "npair"),
+        ("CHORD_B200_PAIR", "pair"),
     ):
         value = os.environ.get(env)
         if value is None:

@@ -68,6 +68,7 @@ struct Options {
   int contiguous_tile = 0; // 0 / 256 = merge neighbouring 128-row blocks of one expert; 128 = do not
   int a_stages = 0;        // 0 = automatic; depth of the TMEM operand ring (2..7)
   int pregather = 1;       // 1 = `indexed` with blocks of >= 64 rows copies the routed rows into slot order first
+  int pair = 1;            // 1 = tiles of more than 128 tokens with consecutive activation rows and K >= 4096 run on clusters of two CTAs (tcgen05.mma.cta_group::2)
   int npair = 1;           // 1 = tiles of <= 128 tokens with consecutive activation rows span two 128-row weight blocks
   int ksplit = 1;          // 1 = layouts with one MMA issuer split small tiles' K halves over two issuers
   int decode_kernel = 1;   // 1 = token tiles of <= 32 rows (indexed, masked) use the warpgroup-per-worker kernel; 0 = never
@@ -96,6 +97,27 @@ inline cudaError_t launch_kernel(void (*kernel)(Params...), dim3 grid, dim3 bloc
   attribute[0].val.programmaticStreamSerializationAllowed = 1;
   config.attrs = attribute;
   config.numAttrs = pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&config, kernel, static_cast<Params>(args)...);
+}
+
+// The same launch as clusters of two CTAs along x (grid.x even).
+template <typename... Params, typename... Args>
+inline cudaError_t launch_kernel_pairs(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem,
+                                       cudaStream_t stream, bool pdl, Args&&... args) {
+  cudaLaunchConfig_t config = {};
+  config.gridDim = grid;
+  config.blockDim = block;
+  config.dynamicSmemBytes = smem;
+  config.stream = stream;
+  cudaLaunchAttribute attribute[2];
+  attribute[0].id = cudaLaunchAttributeClusterDimension;
+  attribute[0].val.clusterDim.x = 2;
+  attribute[0].val.clusterDim.y = 1;
+  attribute[0].val.clusterDim.z = 1;
+  attribute[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute[1].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attribute;
+  config.numAttrs = pdl ? 2 : 1;
   return cudaLaunchKernelEx(&config, kernel, static_cast<Params>(args)...);
 }
 // chord_b200_set_option() writes the options under the exclusive lock; every entry

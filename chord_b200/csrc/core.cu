@@ -90,6 +90,9 @@ int chord_b200_set_option(const char* name, int64_t value) {
   } else if (!std::strcmp(name, "ksplit")) {
     if (value != 0 && value != 1) return fail(kInvalidArgument, "ksplit must be 0 or 1");
     o.ksplit = static_cast<int>(value);
+  } else if (!std::strcmp(name, "pair")) {
+    if (value != 0 && value != 1) return fail(kInvalidArgument, "pair must be 0 or 1");
+    o.pair = static_cast<int>(value);
   } else if (!std::strcmp(name, "npair")) {
     if (value != 0 && value != 1) return fail(kInvalidArgument, "npair must be 0 or 1");
     o.npair = static_cast<int>(value);

@@ -108,6 +108,41 @@ size_t fixed_smem_bytes() { return sizeof(GemmShared) + 1024; }
 
 size_t x_stage_bytes(int mma_n) { return static_cast<size_t>(mma_n) * 256; }
 
+// Clusters of two CTAs of the general kernel that the device keeps resident at once (one
+// per TPC when every TPC has both SMs), looked up once per device and group count.
+template <int kGroups>
+int resident_pairs(size_t smem) {
+  static std::mutex mutex;
+  static int cached[64];
+  static bool have[64];
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess) return 0;
+  std::lock_guard<std::mutex> guard(mutex);
+  if (!have[device & 63]) {
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3(2);
+    config.blockDim = dim3(32 * (12 + 4 * kGroups));
+    config.dynamicSmemBytes = smem;
+    cudaLaunchAttribute attribute[1];
+    attribute[0].id = cudaLaunchAttributeClusterDimension;
+    attribute[0].val.clusterDim.x = 2;
+    attribute[0].val.clusterDim.y = 1;
+    attribute[0].val.clusterDim.z = 1;
+    config.attrs = attribute;
+    config.numAttrs = 1;
+    int clusters = 0;
+    cudaFuncSetAttribute(w4a16_gemm_kernel<kGroups, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                         static_cast<int>(smem));
+    if (cudaOccupancyMaxActiveClusters(&clusters, w4a16_gemm_kernel<kGroups, true>, &config) != cudaSuccess) {
+      cudaGetLastError();
+      clusters = 0;
+    }
+    cached[device & 63] = clusters;
+    have[device & 63] = true;
+  }
+  return cached[device & 63];
+}
+
 // Depth of the activation ring: small tiles get a deep ring cheaply, large
 // ones are limited to what leaves room for the weight ring.
 int pick_x_stages(int mma_n) {
@@ -141,14 +176,24 @@ int launch_with_groups(const CUtensorMap& tm_w, const CUtensorMap& tm_s, const C
     int max_optin = 227 * 1024;
     if (current_device_info(&dev) == kOk) max_optin = dev.max_smem_optin;
     attr_result[device & 63] = cudaFuncSetAttribute(
-        w4a16_gemm_kernel<kGroups>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_optin);
+        w4a16_gemm_kernel<kGroups, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_optin);
+    if (attr_result[device & 63] == cudaSuccess) {
+      attr_result[device & 63] = cudaFuncSetAttribute(
+          w4a16_gemm_kernel<kGroups, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_optin);
+    }
   });
   if (attr_result[device & 63] != cudaSuccess) {
     return fail(kCudaError, "cudaFuncSetAttribute failed: %s",
                 cudaGetErrorString(attr_result[device & 63]));
   }
   const int threads = 32 * (12 + 4 * kGroups);
-  CHORD_CUDA(launch_kernel(w4a16_gemm_kernel<kGroups>, dim3(grid), dim3(threads), smem, stream,
+  if (p.pair) {
+    // every CTA has to be resident (stream-K owners wait for their contributors)
+    CHORD_CUDA(launch_kernel_pairs(w4a16_gemm_kernel<kGroups, true>, dim3(grid), dim3(threads), smem, stream,
+                                   p.pdl != 0, tm_w, tm_s, tm_x, p));
+    return kOk;
+  }
+  CHORD_CUDA(launch_kernel(w4a16_gemm_kernel<kGroups, false>, dim3(grid), dim3(threads), smem, stream,
                            p.pdl != 0, tm_w, tm_s, tm_x, p));
   return kOk;
 }
@@ -188,6 +233,15 @@ int64_t stream_k_bytes(int grid, int mma_n) {
   // blocks (two accumulators), which doubles the slot
   const int64_t general = static_cast<int64_t>(grid) * kBlockN * mma_n * 4 * (mma_n <= 128 ? 2 : 1);
   return (general + 1023) / 1024 * 1024;
+}
+
+// CTA pairs pay off on tiles of more than 128 tokens with a long K loop: a pair MMA costs
+// its issuing thread about 130 cycles whatever its N (measured at 85 and 128 rows per
+// expert: 490 / 505 us on pairs against 388 / 419 us on the two-issuer layout; at 256 and
+// 512 rows: 611 / 1223 us against 726 / 1527 us), and the single 256-column accumulator
+// is drained between tiles with the tensor core idle, which at K = 2048 outweighs the gain.
+bool pair_applies(int mma_n, int n, int k) {
+  return options().pair != 0 && mma_n > 128 && k >= 4096 && (n / kBlockN) % 2 == 0;
 }
 
 bool pregather_applies(int mma_n) { return options().pregather != 0 && mma_n >= 64; }
@@ -350,6 +404,22 @@ int launch_gemm(GemmParams p, const void* x, const int32_t* packed, const void* 
     p.issuers = 2;
     p.ksplit = 0;
   }
+  // Clusters of two CTAs (option "pair") take the same tiles, and 256-token ones, where the
+  // rows are consecutive: one CTA per weight block, half of the token rows each.  Every CTA
+  // must be resident (stream-K owners wait for their contributors), so the grid is cut to
+  // the clusters the device holds at once.
+  int launch_grid = grid;
+  if (pair_applies(p.mma_n, p.n, p.k) && !p.fuse_silu && p.x_load == kXLoadTiled && grid >= 2) {
+    const size_t optin = static_cast<size_t>(dev.max_smem_optin);
+    const int pairs = groups == 4 ? resident_pairs<4>(optin) : resident_pairs<2>(optin);
+    if (pairs >= 1) {
+      p.pair = 1;
+      p.npair = 0;
+      p.ksplit = 0;
+      p.issuers = 1;
+      launch_grid = 2 * (pairs < grid / 2 ? pairs : grid / 2);
+    }
+  }
   CHORD_REQUIRE(!p.fuse_silu || p.npair,
                 "gate_up with fused SiLU*mul needs routing blocks of at most 16 rows, or of 64 to 128 "
                 "rows with the full workspace of chord_b200_indexed_workspace_bytes(); got block_m=%d",
@@ -367,7 +437,12 @@ int launch_gemm(GemmParams p, const void* x, const int32_t* packed, const void* 
   const int turn = groups > p.issuers ? groups : p.issuers;  // both are powers of two
   p.a_stages -= p.a_stages % turn;
   p.w_stages -= p.w_stages % groups;
-  if (p.npair) {
+  if (p.pair) {
+    // half a token tile per CTA: a ring twice as deep in the same shared memory
+    p.x_stages = p.mma_n <= 64 ? 8 : (p.mma_n <= 128 ? 6 : 4);
+    p.w_stages = pick_w_stages(dev, p.mma_n / 2, p.x_stages);
+    p.w_stages -= p.w_stages % groups;
+  } else if (p.npair) {
     // both issuers consume every activation stage (nobody takes turns on that ring), and
     // with two weight stages per activation stage a deeper activation ring is affordable
     p.x_stages = p.mma_n <= 64 ? 6 : 4;
@@ -391,6 +466,11 @@ int launch_gemm(GemmParams p, const void* x, const int32_t* packed, const void* 
   // 256-token layouts load consecutive rows as boxes of 128 (sub-slot ring of the kernel).
   p.x_box_rows = (p.mode == kModeContiguous || p.mma_n == 256) ? 128 : p.mma_n;
   if (p.x_load != kXLoadTiled) p.x_box_rows = p.mma_n;
+  if (p.pair) {
+    // boxes of this CTA's half tile; whole boxes must fit the half (mma_n / 2 rows per K half)
+    const int half = p.mma_n / 2;
+    p.x_box_rows = half <= 64 ? half : (half % 64 == 0 ? 64 : (half % 32 == 0 ? 32 : (half % 16 == 0 ? 16 : 8)));
+  }
   CUtensorMap tm_w, tm_s, tm_x;
   if (int rc = make_map_2d(&tm_w, packed, CU_TENSOR_MAP_DATA_TYPE_INT32, 4,
                            static_cast<uint64_t>(p.n) * 2,
@@ -419,12 +499,12 @@ int launch_gemm(GemmParams p, const void* x, const int32_t* packed, const void* 
                            CU_TENSOR_MAP_SWIZZLE_128B))
     return rc;
 
-  const size_t smem = static_cast<size_t>(p.x_stages) * x_stage_bytes(p.mma_n) +
+  const size_t smem = static_cast<size_t>(p.x_stages) * x_stage_bytes(p.pair ? p.mma_n / 2 : p.mma_n) +
                       static_cast<size_t>(p.w_stages) * (kWStageBytes + kSStageBytes) +
                       fixed_smem_bytes();
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (options().dequant_groups == 4) return launch_with_groups<4>(tm_w, tm_s, tm_x, p, grid, smem, s);
-  return launch_with_groups<2>(tm_w, tm_s, tm_x, p, grid, smem, s);
+  if (options().dequant_groups == 4) return launch_with_groups<4>(tm_w, tm_s, tm_x, p, launch_grid, smem, s);
+  return launch_with_groups<2>(tm_w, tm_s, tm_x, p, launch_grid, smem, s);
 }
 
 // Stream-K scratch that lives in the library image instead of in an allocation:
@@ -696,11 +776,16 @@ int chord_b200_contiguous(const void* x, const int32_t* packed, const void* scal
   // (`npair`).  Where that layout does not apply (option npair = 0, an odd number of
   // weight blocks) or with option contiguous_tile = 256, neighbouring blocks of one
   // expert are merged into 256-token tiles over one weight block instead.
+  bool two_launches = false;
   {
     chord::OptionsReadLock options_guard(chord::options_mutex());
     const chord::Options& o = chord::options();
-    const bool pairs = o.npair != 0 && (n / chord::kBlockN) % 2 == 0;
+    const bool even_blocks = (n / chord::kBlockN) % 2 == 0;
+    const bool pairs = o.npair != 0 && even_blocks;
     p.tile_tokens = o.contiguous_tile == 128 || (o.contiguous_tile == 0 && pairs) ? 128 : 256;
+    // With CTA pairs enabled, experts of more than one 128-row block take 256-token tiles
+    // on CTA pairs in a second launch; single-block experts stay on 128-token tiles.
+    two_launches = o.contiguous_tile == 0 && pairs && chord::pair_applies(256, static_cast<int>(n), static_cast<int>(k));
   }
   p.top_k = 1;
   p.m_blocks = static_cast<int32_t>(m / 128);
@@ -711,6 +796,15 @@ int chord_b200_contiguous(const void* x, const int32_t* packed, const void* scal
   p.workspace = static_cast<float*>(workspace);
   p.locks = locks;
   p.status = status;
+  if (two_launches) {
+    // The launches write disjoint rows and use the scratch and the locks one after the
+    // other (the second launch's kernel waits for the first before it touches either).
+    p.run_max = 1;
+    if (int rc = chord::launch_gemm(p, x, packed, scale, num_locks, workspace_bytes, stream)) return rc;
+    p.tile_tokens = 256;
+    p.run_min = 2;
+    p.run_max = 0;
+  }
   return chord::launch_gemm(p, x, packed, scale, num_locks, workspace_bytes, stream);
 }
 

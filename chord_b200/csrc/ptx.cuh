@@ -515,6 +515,110 @@ __device__ __forceinline__ uint32_t idesc_bf16_f32(uint32_t m, uint32_t n) {
   return d;
 }
 
+// ------------------------------------------------------- CTA pairs (cta_group::2) --
+//
+// Two CTAs of a cluster of two (ranks 0 and 1) on the two SMs of one TPC.  One thread of
+// rank 0 issues tcgen05.mma.cta_group::2: A rows 0-127 come from rank 0's tensor memory
+// and rows 128-255 from rank 1's (same address in both), B rows 0..N/2-1 from rank 0's
+// shared memory and N/2..N-1 from rank 1's (same offset in both), and each CTA receives
+// its 128 rows x N columns of D in its own tensor memory.
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+
+// All threads of both CTAs; orders shared-memory and barrier initialisation before the
+// peer's first access.
+__device__ __forceinline__ void cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+// The shared::cluster address of the same shared-memory location in CTA `rank`.
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+  return r;
+}
+
+// Arrival on a barrier of either CTA of the cluster (address from map_to_cta).
+// Default semantics (as for a local arrival): a cluster-scope release was measured to
+// double the dequant warps' time per stage; what the barrier orders here is tensor memory
+// and TMA-written shared memory, which the tcgen05 fences and the transaction count cover.
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
+}
+
+// Tiled load into this CTA's shared memory whose bytes are counted on a barrier that may
+// live in the peer CTA (address from map_to_cta).  No multicast: each CTA fetches its own
+// rows.
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const void* tmap, uint32_t cluster_bar,
+                                                 int32_t c0, int32_t c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4}], [%2];"
+      :
+      : "r"(dst), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(cluster_bar), "r"(c0), "r"(c1)
+      : "memory");
+}
+
+// Tensor-memory allocation for a CTA pair: the same warp index executes it in both CTAs
+// with the same shared-memory destination; both receive the same column range.
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t dst_smem, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem),
+               "r"(ncols)
+               : "memory");
+}
+
+__device__ __forceinline__ void tmem_relinquish_pair() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols)
+               : "memory");
+}
+
+// mma_ts_k64 for a CTA pair (M = 256 in the instruction descriptor).
+__device__ __forceinline__ void mma_ts_k64_pair(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc,
+                                                uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p, t;\n\t"
+      ".reg .b32 a1, a2, a3;\n\t"
+      ".reg .b64 b1, b2, b3;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "setp.eq.b32 t, 0, 0;\n\t"
+      "add.u32 a1, %1, 8;\n\t"
+      "add.u32 a2, %1, 16;\n\t"
+      "add.u32 a3, %1, 24;\n\t"
+      "add.u64 b1, %2, 2;\n\t"
+      "add.u64 b2, %2, 4;\n\t"
+      "add.u64 b3, %2, 6;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], [%1], %2, %3, p;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], [a1], b1, %3, t;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], [a2], b2, %3, t;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], [a3], b3, %3, t;\n\t"
+      "}\n"
+      :
+      : "r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+// Arrives (count 1) on the barrier at this shared-memory offset in both CTAs of the pair
+// once every pair MMA issued so far by this thread has completed.  (A barrier arrival
+// sent to two CTAs; no data is loaded.)
+__device__ __forceinline__ void mma_commit_pair(uint32_t bar) {
+  asm volatile(
+      "{\n\t"
+      ".reg .b16 m;\n\t"
+      "mov.b16 m, 3;\n\t"
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], m;\n\t"
+      "}\n" ::"r"(bar)
+      : "memory");
+}
+
 // --------------------------------------------------------- global-memory sync --
 
 __device__ __forceinline__ void red_release_add(int* addr, int v) {

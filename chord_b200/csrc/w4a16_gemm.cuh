@@ -117,6 +117,8 @@ struct GemmParams {
   int32_t top_k;        // indexed
   int32_t max_m;        // masked
   int32_t m_blocks;     // contiguous: m / 128
+  int32_t run_min;      // contiguous: only experts whose run of consecutive 128-row blocks has at least
+  int32_t run_max;      //   run_min and (if > 0) at most run_max blocks are computed by this launch
   int32_t x_box_rows;   // tiled activation loads: rows per TMA box
   int32_t sorted_len;   // indexed: capacity of sorted_ids
   int32_t expert_len;   // indexed: capacity of expert_ids
@@ -126,6 +128,7 @@ struct GemmParams {
   int32_t ksplit;       // single-issuer layouts: a second issuer takes the second K half of tiles of <= 128 tokens
   int32_t fuse_silu;    // 1 = gate_up with SiLU*mul in the epilogue: a tile is gate block j and up block j (row N/2 + 128 j), out is [rows, N/2]
   int32_t npair;        // 1 = a tile is two neighbouring 128-row weight blocks sharing one activation stage (tiles of <= 128 tokens)
+  int32_t pair;         // 1 = launched as clusters of two CTAs: a tile is two neighbouring 128-row weight blocks, one per CTA, multiplied by one tcgen05.mma.cta_group::2 stream; each CTA loads half of the tile's token rows
   int32_t a_stages;     // depth of the TMEM A ring; accumulators start at column 64 * a_stages
   int32_t num_locks;
   int32_t pdl;          // host side only: launch with the programmatic stream-serialization attribute
@@ -263,13 +266,16 @@ struct __align__(16) GemmShared {
 };
 
 __device__ __forceinline__ TileInfo decode_tile(const GemmParams& p, const GemmShared& sh,
-                                                int32_t tile) {
+                                                int32_t tile, uint32_t rank = 0) {
   TileInfo t;
   // With `npair` a tile spans two neighbouring 128-row weight blocks (n0 and n0 + 128).
   // With fused SiLU*mul the two blocks are gate block n0 and up block N/2 + n0.
-  const int32_t n_blocks = p.fuse_silu ? (p.n >> 1) / kBlockN : p.n / (kBlockN << p.npair);
+  // With `pair` the two blocks belong to the two CTAs of the cluster: n0 is this CTA's.
+  const int32_t wide = p.npair | p.pair;
+  const int32_t n_blocks = p.fuse_silu ? (p.n >> 1) / kBlockN : p.n / (kBlockN << wide);
   const int32_t mb = tile / n_blocks;
-  t.n0 = (tile - mb * n_blocks) * (p.fuse_silu ? kBlockN : (kBlockN << p.npair));
+  t.n0 = (tile - mb * n_blocks) * (p.fuse_silu ? kBlockN : (kBlockN << wide)) +
+         static_cast<int32_t>(rank) * kBlockN;
   t.m0 = 0;
   t.limit = 0;
   t.mma_n = p.mma_n;
@@ -424,7 +430,7 @@ struct XSubRing {
   __device__ __forceinline__ void flip(uint32_t slot) { phases ^= 1u << slot; }
 };
 
-template <int kDequantGroups>
+template <int kDequantGroups, bool kPair>
 __global__ void __launch_bounds__(32 * (12 + 4 * kDequantGroups), 1)
 w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_s,
                   const __grid_constant__ CUtensorMap tm_x, const GemmParams p) {
@@ -434,7 +440,14 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
   const uint32_t raw_addr = ptx::smem_u32(smem_raw);
   const uint32_t pad = (1024u - (raw_addr & 1023u)) & 1023u;
   uint8_t* smem = smem_raw + pad;
-  const uint32_t x_half_bytes = static_cast<uint32_t>(p.mma_n) * 128u;
+  // `pair`: this CTA is rank 0 (leader: issues the MMAs for both) or 1 of a cluster of two
+  // and holds half of a tile's token rows.
+  // (A kernel that contains cta_group::2 instructions can only be launched as clusters of
+  // two, hence an instantiation of its own.)
+  constexpr bool pair = kPair;
+  uint32_t rank = 0;
+  if constexpr (kPair) rank = ptx::cluster_ctarank();
+  const uint32_t x_half_bytes = (static_cast<uint32_t>(p.mma_n) >> p.pair) * 128u;
   const uint32_t x_stage_bytes = 2u * x_half_bytes;
   const uint32_t w_stages = static_cast<uint32_t>(p.w_stages);
   const uint32_t x_stages = static_cast<uint32_t>(p.x_stages);
@@ -496,21 +509,28 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
       ptx::mbar_init(ptx::smem_u32(&sh.xfull[s]), xfull_count);
       ptx::mbar_init(ptx::smem_u32(&sh.xempty[s]), (ksplit || npair) ? 2 : 1);
     }
+    // `pair`: the leader's afull / dempty collect the arrivals of both CTAs' warps; the
+    // leader's commits reach xempty / aempty / dfull of both CTAs.
     for (uint32_t a = 0; a < 2 * a_stages; ++a) {
-      ptx::mbar_init(ptx::smem_u32(&sh.afull[a]), 4);
+      ptx::mbar_init(ptx::smem_u32(&sh.afull[a]), pair ? 8 : 4);
       ptx::mbar_init(ptx::smem_u32(&sh.aempty[a]), 1);
     }
     for (uint32_t d = 0; d < 2; ++d) {
       ptx::mbar_init(ptx::smem_u32(&sh.dfull[d]), ni);
-      ptx::mbar_init(ptx::smem_u32(&sh.dempty[d]), 4);
+      ptx::mbar_init(ptx::smem_u32(&sh.dempty[d]), pair ? 8 : 4);
     }
     sh.abort_flag = 0;
     sh.epilogue_failed = 0;
     ptx::fence_barrier_init();
   }
   if (warp == 2) {
-    ptx::tmem_alloc(ptx::smem_u32(&sh.tmem_base), kTmemCols);
-    ptx::tmem_relinquish();
+    if constexpr (kPair) {
+      ptx::tmem_alloc_pair(ptx::smem_u32(&sh.tmem_base), kTmemCols);
+      ptx::tmem_relinquish_pair();
+    } else {
+      ptx::tmem_alloc(ptx::smem_u32(&sh.tmem_base), kTmemCols);
+      ptx::tmem_relinquish();
+    }
   }
   // Token slots no load ever fills must not hold NaN patterns.
   for (uint32_t i = threadIdx.x; i < x_stages * x_stage_bytes / 16; i += blockDim.x) {
@@ -575,18 +595,29 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
     __syncthreads();
     if (threadIdx.x == 0) {
       int32_t count = 0;
+      int32_t run_end = 0;  // one past the current expert's run of blocks
       for (int32_t i = 0; i < p.m_blocks;) {
         const int32_t e = static_cast<int32_t>(sh.mtile[i]);
         if (e < 0 || e >= p.num_experts) {
           ++i;
           continue;
         }
-        const bool pair = p.tile_tokens == 256 && i + 1 < p.m_blocks &&
-                          static_cast<int32_t>(sh.mtile[i + 1]) == e;
-        sh.tile_rows[count] = pair ? static_cast<uint16_t>(128 + sh.tile_rows[i + 1]) : sh.tile_rows[i];
+        if (i >= run_end) {
+          // A new run: this launch takes it whole or leaves it whole to another launch.
+          run_end = i + 1;
+          while (run_end < p.m_blocks && static_cast<int32_t>(sh.mtile[run_end]) == e) ++run_end;
+          const int32_t run = run_end - i;
+          if (run < p.run_min || (p.run_max > 0 && run > p.run_max)) {
+            i = run_end;
+            continue;
+          }
+        }
+        const bool merged = p.tile_tokens == 256 && i + 1 < p.m_blocks &&
+                            static_cast<int32_t>(sh.mtile[i + 1]) == e;
+        sh.tile_rows[count] = merged ? static_cast<uint16_t>(128 + sh.tile_rows[i + 1]) : sh.tile_rows[i];
         sh.mtile[count++] = static_cast<uint32_t>(e) | (static_cast<uint32_t>(i) << 15) |
-                            (pair ? 0x80000000u : 0u);
-        i += pair ? 2 : 1;
+                            (merged ? 0x80000000u : 0u);
+        i += merged ? 2 : 1;
       }
       sh.m_blocks = count;
     }
@@ -594,15 +625,24 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
   ptx::fence_proxy_async();
   ptx::tc_fence_before();
   __syncthreads();
+  // the peer's barriers must be initialised before anything arrives on them
+  if constexpr (kPair) ptx::cluster_sync();
   ptx::tc_fence_after();
   ptx::grid_launch_dependents();
 
   const uint32_t tmem_base = __shfl_sync(0xffffffffu, sh.tmem_base, 0);  // uniform, see `warp`
   volatile uint32_t* abort_flag = &sh.abort_flag;
+  // Offset that turns a shared-memory address of this CTA into the cluster address of the
+  // same location in the leader (rank 0).
+  const uint32_t sh_addr = ptx::smem_u32(&sh);
+  uint32_t to_leader = 0;
+  if constexpr (kPair) to_leader = ptx::map_to_cta(sh_addr, 0) - sh_addr;
   const int32_t tiles = __shfl_sync(0xffffffffu, sh.m_blocks, 0) *
-                        (p.fuse_silu ? (p.n >> 1) / kBlockN : p.n / (kBlockN << p.npair));
+                        (p.fuse_silu ? (p.n >> 1) / kBlockN : p.n / (kBlockN << (p.npair | p.pair)));
+  // Both CTAs of a pair walk the same sequence of tiles.
   SegmentIterator iter;
-  iter.init(tiles, k_iters, static_cast<int32_t>(gridDim.x), static_cast<int32_t>(blockIdx.x));
+  iter.init(tiles, k_iters, static_cast<int32_t>(gridDim.x >> p.pair),
+            static_cast<int32_t>(blockIdx.x >> p.pair));
   Segment seg;
 
   if (warp == 0 || warp == 1) {
@@ -617,7 +657,7 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
       StageCursor cur;
       bool ok = true;
       while (ok && iter.next(seg)) {
-        const TileInfo t = decode_tile(p, sh, seg.tile);
+        const TileInfo t = decode_tile(p, sh, seg.tile, rank);
         if (!t.valid) continue;
         const int32_t col = weights ? 2 * t.n0 : t.n0;
         // to the tile's second weight block: the next 128 rows, or the up rows of a fused gate_up
@@ -652,24 +692,26 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
     if (p.x_load == kXLoadTiled) {
       // Consecutive rows: one box per 64-wide K half, issued by one thread.
       while (ok && threadIdx.x == 64 && iter.next(seg)) {
-        const TileInfo t = decode_tile(p, sh, seg.tile);
+        const TileInfo t = decode_tile(p, sh, seg.tile, rank);
         if (!t.valid) continue;
         int32_t k_col = seg.kb * kBlockK;
-        const int32_t x_row0 = t.base + t.m0;
-        const int32_t boxes = (t.mma_n + p.x_box_rows - 1) / p.x_box_rows;
-        const bool pair = t.mma_n > 128;
+        // `pair`: this CTA's half of the tile's token rows
+        const int32_t tile_rows_here = t.mma_n >> p.pair;
+        const int32_t x_row0 = t.base + t.m0 + static_cast<int32_t>(rank) * tile_rows_here;
+        const int32_t boxes = (tile_rows_here + p.x_box_rows - 1) / p.x_box_rows;
+        const bool two_slots = t.mma_n > 128;
         for (int32_t kb = seg.kb; kb < seg.ke; ++kb) {
           if (subslots) {
-            const uint32_t s0 = xring.take(pair, 2u * x_stages);
+            const uint32_t s0 = xring.take(two_slots, 2u * x_stages);
             if (!ptx::mbar_wait(ptx::smem_u32(&sh.xempty[s0]), xring.phase(s0) ^ 1u, abort_flag) ||
-                (pair && !ptx::mbar_wait(ptx::smem_u32(&sh.xempty[s0 + 1]), xring.phase(s0 + 1) ^ 1u,
-                                         abort_flag))) {  // odd half: checked, not consumed
+                (two_slots && !ptx::mbar_wait(ptx::smem_u32(&sh.xempty[s0 + 1]), xring.phase(s0 + 1) ^ 1u,
+                                              abort_flag))) {  // odd half: checked, not consumed
               ok = false;
               break;
             }
             const uint32_t full = ptx::smem_u32(&sh.xfull[s0]);
             const uint32_t xs = ptx::smem_u32(smem_x + s0 * kSubBytes);
-            const uint32_t half = pair ? kSubBytes : kSubBytes / 2;  // bytes of one K half
+            const uint32_t half = two_slots ? kSubBytes : kSubBytes / 2;  // bytes of one K half
             ptx::mbar_arrive_expect_tx(full, static_cast<uint32_t>(boxes) * kSubBytes);
             for (int32_t b = 0; b < boxes; ++b) {
               const uint32_t off = static_cast<uint32_t>(b) * (kSubBytes / 2);
@@ -686,6 +728,24 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
           }
           const uint32_t full = ptx::smem_u32(&sh.xfull[cur.s]);
           const uint32_t xs = ptx::smem_u32(smem_x + cur.s * x_stage_bytes);
+          if constexpr (kPair) {
+            // Both CTAs' boxes are counted on the leader's barrier, which expects the bytes
+            // of both halves.  (A box of the peer that lands before the leader's arrival
+            // only drives the transaction count negative for a moment: the phase cannot
+            // complete before that arrival.)
+            if (rank == 0) {
+              ptx::mbar_arrive_expect_tx(full, 2u * static_cast<uint32_t>(boxes * p.x_box_rows) * 256u);
+            }
+            for (int32_t b = 0; b < boxes; ++b) {
+              const uint32_t off = static_cast<uint32_t>(b * p.x_box_rows) * 128u;
+              ptx::tma_load_2d_pair(xs + off, &tm_x, full + to_leader, k_col, x_row0 + b * p.x_box_rows);
+              ptx::tma_load_2d_pair(xs + x_half_bytes + off, &tm_x, full + to_leader, k_col + 64,
+                                    x_row0 + b * p.x_box_rows);
+            }
+            k_col += kBlockK;
+            cur.advance(x_stages);
+            continue;
+          }
           ptx::mbar_arrive_expect_tx(full, static_cast<uint32_t>(boxes * p.x_box_rows) * 256u);
           for (int32_t b = 0; b < boxes; ++b) {
             const uint32_t off = static_cast<uint32_t>(b * p.x_box_rows) * 128u;
@@ -701,7 +761,7 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
       // Routed rows by TMA: four rows per instruction, lanes of warp 2 own the row
       // groups lane and lane + 32.
       while (ok && warp == 2 && iter.next(seg)) {
-        const TileInfo t = decode_tile(p, sh, seg.tile);
+        const TileInfo t = decode_tile(p, sh, seg.tile, rank);
         if (!t.valid) continue;
         int32_t rows[2][4];
         const int32_t load_groups = (t.ntok + 3) >> 2;
@@ -755,7 +815,7 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
       // A warp whose bounded wait ran out stops copying but keeps walking the tiles, so
       // that its sibling never waits alone at the three barriers below.
       while (iter.next(seg)) {
-        const TileInfo t = decode_tile(p, sh, seg.tile);
+        const TileInfo t = decode_tile(p, sh, seg.tile, rank);
         if (!t.valid) continue;
         ptx::named_bar_sync(2, kHelperThreads);  // readers of the previous tile's rows are done
         // Element offset of each slot's activation row, or -1 for a slot without a token;
@@ -850,7 +910,7 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
   } else if (warp < kFirstDequantWarp) {
     // ----------------------------------------------------------- MMA issuers --
     const uint32_t me = warp - kFirstIssuerWarp;
-    if (me < ni && lane == 0) {
+    if (me < ni && lane == 0 && rank == 0) {
       const uint64_t xdesc0 = ptx::smem_desc_k_sw128(ptx::smem_u32(smem_x));
       const uint64_t xdesc_stage = x_stage_bytes >> 4;  // descriptor address units are 16 bytes
       const uint64_t xdesc_half = x_half_bytes >> 4;
@@ -860,7 +920,7 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
       uint32_t it = 0, segc = 0;
       bool ok = true;
       while (ok && iter.next(seg)) {
-        const TileInfo t = decode_tile(p, sh, seg.tile);
+        const TileInfo t = decode_tile(p, sh, seg.tile, rank);
         if (!t.valid) continue;
         const uint32_t d = d_bufs == 2 ? (segc & 1u) : 0u;
         const uint32_t dph = d_bufs == 2 ? ((segc >> 1) & 1u) : (segc & 1u);
@@ -870,11 +930,39 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
         }
         ptx::tc_fence_after();
         const uint32_t d_addr = tmem_base + d_col0 + (d * ni + me) * d_cols;
-        const uint32_t idesc = ptx::idesc_bf16_f32(kBlockN, static_cast<uint32_t>(t.mma_n));
+        const uint32_t idesc = ptx::idesc_bf16_f32(kBlockN << p.pair, static_cast<uint32_t>(t.mma_n));
         uint32_t acc = 0;
         const bool split = ksplit && t.mma_n <= 128;
         for (int32_t kb = seg.kb; kb < seg.ke; ++kb, ++it) {
-          if (npair) {
+          if constexpr (kPair) {
+            // One MMA stream for both CTAs; every commit arrives on the barrier of each.
+            const uint32_t a = acur.s << 1;
+            const uint32_t aph = acur.ph;
+            if (!ptx::mbar_wait(ptx::smem_u32(&sh.xfull[cur.s]), cur.ph, abort_flag)) {
+              ok = false;
+              break;
+            }
+            const uint32_t a_addr = tmem_base + acur.s * kAColsPerStage;
+            if (!ptx::mbar_wait(ptx::smem_u32(&sh.afull[a]), aph, abort_flag)) {
+              ok = false;
+              break;
+            }
+            ptx::tc_fence_after();
+            ptx::mma_ts_k64_pair(d_addr, a_addr, xdesc, idesc, acc);
+            const uint32_t ae = ptx::smem_u32(&sh.aempty[a]);
+            ptx::mma_commit_pair(ae);
+            if (!ptx::mbar_wait(ptx::smem_u32(&sh.afull[a + 1]), aph, abort_flag)) {
+              ok = false;
+              break;
+            }
+            ptx::tc_fence_after();
+            if (!(k_tail_half && kb == k_iters - 1)) {
+              ptx::mma_ts_k64_pair(d_addr, a_addr + 32, xdesc + xdesc_half, idesc, 1);
+            }
+            acc = 1;
+            ptx::mma_commit_pair(ae + 8u);
+            ptx::mma_commit_pair(ptx::smem_u32(&sh.xempty[cur.s]));
+          } else if (npair) {
             // The K block's two operand-ring entries belong to the tile's two weight blocks;
             // this issuer takes the one of its block, with both K halves, into its accumulator.
             uint32_t as = acur.s + me, aph = acur.ph;
@@ -912,11 +1000,11 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
             const uint32_t aph = acur.ph;
             uint32_t xslot = cur.s;       // barrier (and, with sub-slots, buffer) of this stage
             uint64_t xd = xdesc, xd_half = xdesc_half;
-            const bool pair = subslots && t.mma_n > 128;
+            const bool two_slots = subslots && t.mma_n > 128;
             if (subslots) {
-              xslot = xring.take(pair, 2u * x_stages);
+              xslot = xring.take(two_slots, 2u * x_stages);
               xd = xdesc0 + xslot * (kSubBytes >> 4);
-              xd_half = pair ? (kSubBytes >> 4) : (kSubBytes >> 5);
+              xd_half = two_slots ? (kSubBytes >> 4) : (kSubBytes >> 5);
               if (!ptx::mbar_wait(ptx::smem_u32(&sh.xfull[xslot]), xring.phase(xslot), abort_flag)) {
                 ok = false;
                 break;
@@ -1004,8 +1092,13 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
         }
         if (!ok) break;
         // One arrival per issuer and segment, also from an issuer that had no stage in it.
-        if (acc != 0) ptx::mma_commit(ptx::smem_u32(&sh.dfull[d]));
-        else ptx::mbar_arrive(ptx::smem_u32(&sh.dfull[d]));
+        if constexpr (kPair) {
+          ptx::mma_commit_pair(ptx::smem_u32(&sh.dfull[d]));
+        } else if (acc != 0) {
+          ptx::mma_commit(ptx::smem_u32(&sh.dfull[d]));
+        } else {
+          ptx::mbar_arrive(ptx::smem_u32(&sh.dfull[d]));
+        }
         ++segc;
       }
       if (!ok) {
@@ -1035,7 +1128,11 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
         ptx::tmem_wait_st();
         ptx::tc_fence_before();
         __syncwarp();
-        if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&sh.afull[pending]));
+        if (lane == 0) {
+          // `pair`: the leader's barrier counts the warps of both CTAs
+          if constexpr (kPair) ptx::mbar_arrive_cluster(ptx::smem_u32(&sh.afull[pending]) + to_leader);
+          else ptx::mbar_arrive(ptx::smem_u32(&sh.afull[pending]));
+        }
         pending = -1;
       }
     };
@@ -1077,7 +1174,7 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
       return true;
     };
     while (ok && iter.next(seg)) {
-      const TileInfo t = decode_tile(p, sh, seg.tile);
+      const TileInfo t = decode_tile(p, sh, seg.tile, rank);
       if (!t.valid) continue;
       // This group owns the stages whose running index is `group` modulo the number
       // of groups: step over the others without visiting them.
@@ -1148,7 +1245,7 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
     const size_t ws_block = static_cast<size_t>(kBlockN) * p.mma_n;  // partial sums of one weight block
     const size_t ws_slot = ws_block * w_per_kb;
     while (ok && iter.next(seg)) {
-      const TileInfo t = decode_tile(p, sh, seg.tile);
+      const TileInfo t = decode_tile(p, sh, seg.tile, rank);
       if (!t.valid) continue;
       const uint32_t d = d_bufs == 2 ? (segc & 1u) : 0u;
       const uint32_t dph = d_bufs == 2 ? ((segc >> 1) & 1u) : (segc & 1u);
@@ -1158,7 +1255,7 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
       bool lock_ok = true;
       if (seg.type == kSegOwner && et == 0) {
         // Wait (bounded) until every other slice of this tile has published its partial.
-        const int* lock = p.locks + blockIdx.x;
+        const int* lock = p.locks + blockIdx.x;  // (`pair`: one word per CTA; the slices of its rows come from CTAs of its own rank)
         lock_ok = false;
         for (int32_t spin = 0; spin < p.lock_spins; ++spin) {
           if (ptx::ld_acquire(lock) >= seg.peer) {
@@ -1241,7 +1338,7 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
         }
         if (seg.type == kSegOwner && computed) {
           for (int32_t peer = 1; peer <= seg.peer; ++peer) {
-            const float* src = p.workspace + (blockIdx.x + peer) * ws_slot + ws_sub +
+            const float* src = p.workspace + (blockIdx.x + (peer << p.pair)) * ws_slot + ws_sub +
                                static_cast<size_t>(c0) * kBlockN + et;
 #pragma unroll
             for (int j = 0; j < 16; ++j) acc[j] += __ldcg(src + j * kBlockN);
@@ -1285,11 +1382,15 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
       // Release the accumulator buffer to the MMA issuer.
       ptx::tc_fence_before();
       __syncwarp();
-      if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&sh.dempty[d]));
+      if (lane == 0) {
+        if constexpr (kPair) ptx::mbar_arrive_cluster(ptx::smem_u32(&sh.dempty[d]) + to_leader);
+        else ptx::mbar_arrive(ptx::smem_u32(&sh.dempty[d]));
+      }
       if (seg.type == kSegContrib) {
         __threadfence();
         ptx::named_bar_sync(1, 128);
-        if (et == 0) ptx::red_release_add(p.locks + seg.peer, 1);
+        // the owner of this CTA's rows: the CTA of the same rank in the owning pair
+        if (et == 0) ptx::red_release_add(p.locks + ((seg.peer << p.pair) + static_cast<int32_t>(rank)), 1);
       } else if (seg.type == kSegOwner) {
         ptx::named_bar_sync(1, 128);
         // After a timeout the word is left as it is: contributors that arrive late would
@@ -1309,9 +1410,13 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
   // --------------------------------------------------------------- teardown --
   ptx::tc_fence_before();
   __syncthreads();
+  // `pair`: neither CTA may leave (or free tensor memory) while the other can still
+  // signal its barriers or have MMAs reading its shared and tensor memory.
+  if constexpr (kPair) ptx::cluster_sync();
   if (warp == 2) {
     ptx::tc_fence_after();
-    ptx::tmem_dealloc(tmem_base, kTmemCols);
+    if constexpr (kPair) ptx::tmem_dealloc_pair(tmem_base, kTmemCols);
+    else ptx::tmem_dealloc(tmem_base, kTmemCols);
   }
 }
 

@@ -143,15 +143,17 @@ def test_grouped_argument_checks(device):
                               torch.zeros(64, dtype=torch.int32, device=device))
 
 
-@pytest.mark.parametrize("option,value", [("ksplit", 0), ("contiguous_tile", 256), ("npair", 0), ("decode_kernel", 0)])
+@pytest.mark.parametrize("option,value", [("ksplit", 0), ("contiguous_tile", 256), ("npair", 0), ("decode_kernel", 0),
+                                          ("pair", 0)])
 def test_grouped_kernel_variants(device, option, value):
-    """Without the second MMA issuer / with merged 256-token tiles over one weight block /
-    with one weight block per tile / with small masked tiles on the general kernel: same
-    results within tolerance."""
+    """Without the second MMA issuer / with merged 256-token tiles (on CTA pairs) for every
+    expert / with one weight block per tile / with small masked tiles on the general kernel /
+    without CTA pairs (256-token tiles on one CTA, `contiguous` in one launch): same results
+    within tolerance."""
     import chord_b200
     from chord_b200 import _lib
 
-    defaults = {"ksplit": 1, "contiguous_tile": 0, "npair": 1, "decode_kernel": 1}
+    defaults = {"ksplit": 1, "contiguous_tile": 0, "npair": 1, "decode_kernel": 1, "pair": 1}
     ccase = make_contiguous_case([5, 300, 0, 128, 77, 513], 512, 640, seed=31)
     mcase = make_masked_case(6, 200, 256, 384, 16, seed=32)
     mcase["masked_m"] = torch.tensor([0, 3, 16, 33, 150, 200], dtype=torch.int32)
@@ -214,3 +216,35 @@ def test_contiguous_matches_the_references_own_test_vectors(device, name):
     assert bool((got[pad] == ref[pad]).all())
     assert O.cosine_diff(got[~pad], ref[~pad]) < c["cosine_limit"]
     assert O.max_abs_rel(got[~pad], ref[~pad]) <= REL_LIMIT
+
+
+def test_cta_pairs_agree_with_single_ctas(device):
+    """Experts of several 128-row blocks run as 256-token tiles on clusters of two CTAs
+    (tcgen05.mma.cta_group::2, half of the token rows loaded by each CTA) in a launch of their
+    own; single-block experts keep the 128-token layout.  Against the same call without CTA
+    pairs: the same rows written, values equal up to the order of the stream-K partial sums,
+    status word clear, locks back at zero, twice in a row."""
+    import chord_b200
+    from chord_b200 import _lib
+    from chord_b200.indexed_gemm import default_locks
+
+    case = make_contiguous_case([256, 40, 700, 0, 128, 129, 1], 1024, 1152, seed=77)
+    w = chord_b200.pack_w4a16(case["codes"].to(device), case["scale"].to(device))
+    x2, m_indices = case["x2"].to(device), case["m_indices"].to(device)
+    outs = {}
+    try:
+        for pair in (0, 1):
+            _lib.set_option("pair", pair)
+            for _ in range(2):
+                out = torch.full((x2.size(0), 1024), float("nan"), dtype=torch.bfloat16, device=device)
+                chord_b200.contiguous(x2, w, m_indices, outputs=out)
+                _status_ok(device)
+            assert bool((default_locks(device) == 0).all())
+            outs[pair] = out.float().cpu()
+    finally:
+        _lib.set_option("pair", 1)
+    assert torch.equal(torch.isnan(outs[0]), torch.isnan(outs[1]))
+    a, b = outs[0].nan_to_num(), outs[1].nan_to_num()
+    assert float((a == b).float().mean()) >= 0.995
+    assert float((a - b).abs().max()) <= 2.0 ** -6 * float(a.abs().max())
+    _compare(outs[1].to(torch.bfloat16), O.reference_contiguous(case["x2"], case["codes"], case["scale"], case["m_indices"]))
