@@ -68,7 +68,7 @@ struct Options {
   int contiguous_tile = 0; // 0 / 256 = merge neighbouring 128-row blocks of one expert; 128 = do not
   int a_stages = 0;        // 0 = automatic; depth of the TMEM operand ring (2..7)
   int pregather = 1;       // 1 = `indexed` with blocks of >= 64 rows copies the routed rows into slot order first
-  int pair = 1;            // 1 = tiles of more than 128 tokens with consecutive activation rows and K >= 4096 run on clusters of two CTAs (tcgen05.mma.cta_group::2)
+  int pair = 1;            // 1 = tiles of more than 128 tokens with consecutive activation rows and K >= 2048 run on clusters of two CTAs (tcgen05.mma.cta_group::2)
   int npair = 1;           // 1 = tiles of <= 128 tokens with consecutive activation rows span two 128-row weight blocks
   int ksplit = 1;          // 1 = layouts with one MMA issuer split small tiles' K halves over two issuers
   int decode_kernel = 1;   // 1 = token tiles of <= 32 rows (indexed, masked) use the warpgroup-per-worker kernel; 0 = never

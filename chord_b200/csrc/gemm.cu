@@ -235,13 +235,13 @@ int64_t stream_k_bytes(int grid, int mma_n) {
   return (general + 1023) / 1024 * 1024;
 }
 
-// CTA pairs pay off on tiles of more than 128 tokens with a long K loop: a pair MMA costs
-// its issuing thread about 130 cycles whatever its N (measured at 85 and 128 rows per
-// expert: 490 / 505 us on pairs against 388 / 419 us on the two-issuer layout; at 256 and
-// 512 rows: 611 / 1223 us against 726 / 1527 us), and the single 256-column accumulator
-// is drained between tiles with the tensor core idle, which at K = 2048 outweighs the gain.
+// CTA pairs pay off on tiles of more than 128 tokens: a pair MMA costs its issuing thread
+// about 130 cycles whatever its N (measured at 85 and 128 rows per expert: 490 / 505 us on
+// pairs against 388 / 419 us on the two-issuer layout; at 256 and 512 rows: 591 / 1131 us
+// against 720 / 1386 us).  The single 256-column accumulator is drained between tiles with
+// the tensor core idle, so very short K loops are left to single CTAs.
 bool pair_applies(int mma_n, int n, int k) {
-  return options().pair != 0 && mma_n > 128 && k >= 4096 && (n / kBlockN) % 2 == 0;
+  return options().pair != 0 && mma_n > 128 && k >= 2048 && (n / kBlockN) % 2 == 0;
 }
 
 bool pregather_applies(int mma_n) { return options().pregather != 0 && mma_n >= 64; }

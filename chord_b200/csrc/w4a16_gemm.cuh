@@ -252,7 +252,7 @@ struct __align__(16) GemmShared {
   volatile uint32_t epilogue_failed;
   int32_t x_slots;                   // helpers: token slots of the current tile that carry a row
   int32_t out_row[kMaxTileTokens];   // epilogue: output row per token slot, -1 = skip
-  __align__(16) __nv_bfloat16 stage[4][16][32];  // epilogue: per-warp transpose buffer
+  __align__(16) __nv_bfloat16 stage[8][16][32];  // epilogue: per-warp transpose buffer (second set: the pair kernel's second epilogue group)
   int32_t x_row[kMaxTileTokens];     // producer (cp.async variant): activation row per slot
   int32_t group_prefix[kMaxGroups + 1];  // masked: first M tile of each group
   // contiguous: M tiles after merging neighbouring 128-row blocks of one expert:
@@ -509,15 +509,16 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
       ptx::mbar_init(ptx::smem_u32(&sh.xfull[s]), xfull_count);
       ptx::mbar_init(ptx::smem_u32(&sh.xempty[s]), (ksplit || npair) ? 2 : 1);
     }
-    // `pair`: the leader's afull / dempty collect the arrivals of both CTAs' warps; the
-    // leader's commits reach xempty / aempty / dfull of both CTAs.
+    // `pair`: the leader's afull / dempty collect the arrivals of both CTAs' warps (four
+    // dequant warps per stage, eight epilogue warps per CTA); the leader's commits reach
+    // xempty / aempty / dfull of both CTAs.
     for (uint32_t a = 0; a < 2 * a_stages; ++a) {
       ptx::mbar_init(ptx::smem_u32(&sh.afull[a]), pair ? 8 : 4);
       ptx::mbar_init(ptx::smem_u32(&sh.aempty[a]), 1);
     }
     for (uint32_t d = 0; d < 2; ++d) {
       ptx::mbar_init(ptx::smem_u32(&sh.dfull[d]), ni);
-      ptx::mbar_init(ptx::smem_u32(&sh.dempty[d]), pair ? 8 : 4);
+      ptx::mbar_init(ptx::smem_u32(&sh.dempty[d]), pair ? 16 : 4);
     }
     sh.abort_flag = 0;
     sh.epilogue_failed = 0;
@@ -684,7 +685,7 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
       }
     }
     __syncwarp();
-  } else if (warp < kFirstIssuerWarp) {
+  } else if (warp < kFirstIssuerWarp && !(kPair && warp == 3)) {
     // ------------------------------------------------ warps 2-3: activations --
     StageCursor cur;
     XSubRing xring;
@@ -907,9 +908,11 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
       sh.abort_flag = 1;
       if (p.status) atomicOr(p.status, kStatusProducerTimeout);
     }
-  } else if (warp < kFirstDequantWarp) {
+  } else if (kPair ? warp == 3 : warp < kFirstDequantWarp) {
     // ----------------------------------------------------------- MMA issuers --
-    const uint32_t me = warp - kFirstIssuerWarp;
+    // (The pair kernel's single issuer sits in warp 3, which has nothing else to do when
+    // the activation rows are consecutive; warps 4-7 are its second epilogue group.)
+    const uint32_t me = kPair ? 0u : warp - kFirstIssuerWarp;
     if (me < ni && lane == 0 && rank == 0) {
       const uint64_t xdesc0 = ptx::smem_desc_k_sw128(ptx::smem_u32(smem_x));
       const uint64_t xdesc_stage = x_stage_bytes >> 4;  // descriptor address units are 16 bytes
@@ -1107,7 +1110,7 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
       }
     }
     __syncwarp();
-  } else if (warp < kFirstEpilogueWarp) {
+  } else if (warp >= kFirstDequantWarp && warp < kFirstEpilogueWarp) {
     // --------------------------------------------------------------- dequant --
     const uint32_t group = (warp - kFirstDequantWarp) >> 2;
     const uint32_t q = warp & 3;  // TMEM lane quarter == 32 weight rows
@@ -1238,8 +1241,14 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
     }
   } else {
     // -------------------------------------------------------------- epilogue --
+    // Four warps, one per tensor-memory lane quarter; the pair kernel has a second group
+    // of four (warps 4-7) that takes every other 16-column chunk: its 256-column
+    // accumulator is single-buffered, so the tensor core idles while it is drained.
     const uint32_t q = warp & 3;
-    const uint32_t et = threadIdx.x - kFirstEpilogueWarp * 32;  // 0..127 == TMEM lane
+    constexpr uint32_t kEpiThreads = kPair ? 256u : 128u;
+    const uint32_t egroup = (kPair && warp < kFirstDequantWarp) ? 1u : 0u;
+    const uint32_t et = threadIdx.x - (egroup ? kFirstIssuerWarp : kFirstEpilogueWarp) * 32;  // 0..127 == TMEM lane
+    const uint32_t efill = egroup * 128u + et;  // index among all epilogue threads
     uint32_t segc = 0, it0 = 0;
     bool ok = true;
     const size_t ws_block = static_cast<size_t>(kBlockN) * p.mma_n;  // partial sums of one weight block
@@ -1249,11 +1258,11 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
       if (!t.valid) continue;
       const uint32_t d = d_bufs == 2 ? (segc & 1u) : 0u;
       const uint32_t dph = d_bufs == 2 ? ((segc >> 1) & 1u) : (segc & 1u);
-      ptx::named_bar_sync(1, 128);  // previous segment's out_row readers are done
+      ptx::named_bar_sync(1, kEpiThreads);  // previous segment's out_row readers are done
       const int32_t row_slots = (t.rows + 15) & ~15;  // >= t.mma_n; beyond it: rows written as zeros
-      for (int32_t c = et; c < row_slots; c += 128) sh.out_row[c] = out_row_of(p, t, c);
+      for (int32_t c = efill; c < row_slots; c += kEpiThreads) sh.out_row[c] = out_row_of(p, t, c);
       bool lock_ok = true;
-      if (seg.type == kSegOwner && et == 0) {
+      if (seg.type == kSegOwner && efill == 0) {
         // Wait (bounded) until every other slice of this tile has published its partial.
         const int* lock = p.locks + blockIdx.x;  // (`pair`: one word per CTA; the slices of its rows come from CTAs of its own rank)
         lock_ok = false;
@@ -1272,7 +1281,7 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
         sh.epilogue_failed = 1;
       }
       ptx::tc_fence_after();
-      ptx::named_bar_sync(1, 128);  // out_row filled, lock observed, verdict published
+      ptx::named_bar_sync(1, kEpiThreads);  // out_row filled, lock observed, verdict published
       if (sh.epilogue_failed != 0) {
         ok = false;
         break;
@@ -1290,7 +1299,7 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
       const int32_t n_sub = t.n0 + sub * kBlockN + static_cast<int32_t>(q) * 32;
       __nv_bfloat16* out_tile = p.out + n_sub;
       const size_t ws_sub = static_cast<size_t>(sub) * ws_block;
-      for (int32_t c0 = 0; c0 < row_slots; c0 += 16) {
+      for (int32_t c0 = static_cast<int32_t>(egroup) * 16; c0 < row_slots; c0 += kPair ? 32 : 16) {
         float acc[16];
 #pragma unroll
         for (int j = 0; j < 16; ++j) acc[j] = 0.0f;
@@ -1355,7 +1364,7 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
         // Transpose through shared memory so that global stores are 16 bytes wide: the
         // warp holds 32 weight rows x 16 tokens (one token per register); staged as
         // [token][row], each lane then stores two 8-row pieces of a token's 64 bytes.
-        __nv_bfloat16* stage = &sh.stage[q][0][0];
+        __nv_bfloat16* stage = &sh.stage[egroup * 4u + q][0][0];
 #pragma unroll
         for (int j = 0; j < 16; ++j) stage[j * 32 + lane] = __float2bfloat16_rn(acc[j]);
         __syncwarp();
@@ -1388,15 +1397,15 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
       }
       if (seg.type == kSegContrib) {
         __threadfence();
-        ptx::named_bar_sync(1, 128);
+        ptx::named_bar_sync(1, kEpiThreads);
         // the owner of this CTA's rows: the CTA of the same rank in the owning pair
-        if (et == 0) ptx::red_release_add(p.locks + ((seg.peer << p.pair) + static_cast<int32_t>(rank)), 1);
+        if (efill == 0) ptx::red_release_add(p.locks + ((seg.peer << p.pair) + static_cast<int32_t>(rank)), 1);
       } else if (seg.type == kSegOwner) {
-        ptx::named_bar_sync(1, 128);
+        ptx::named_bar_sync(1, kEpiThreads);
         // After a timeout the word is left as it is: contributors that arrive late would
         // otherwise leave it non-zero behind a reset, and the caller has to clear the
         // buffer anyway once the status word reports the failure.
-        if (et == 0 && lock_ok) p.locks[blockIdx.x] = 0;
+        if (efill == 0 && lock_ok) p.locks[blockIdx.x] = 0;
       }
       ++segc;
       it0 += seg_len;

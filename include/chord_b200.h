@@ -62,7 +62,7 @@ const char* chord_b200_version(void);
  *                     rows span two neighbouring 128-row weight blocks, so that an
  *                     activation stage is fetched once per 256 weight rows; 0 one block
  *   "pair"            1 (default) tiles of more than 128 tokens with consecutive activation
- *                     rows and K >= 4096 run on clusters of two CTAs: one tcgen05.mma.cta_group::2 stream
+ *                     rows and K >= 2048 run on clusters of two CTAs: one tcgen05.mma.cta_group::2 stream
  *                     multiplies two neighbouring 128-row weight blocks (one per CTA) and each
  *                     CTA loads half of the token rows (no multicast); `contiguous` then takes
  *                     two launches, experts of one 128-row block on 128-token tiles and the

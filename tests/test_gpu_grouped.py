@@ -219,19 +219,25 @@ def test_contiguous_matches_the_references_own_test_vectors(device, name):
 
 
 def test_cta_pairs_agree_with_single_ctas(device):
-    """Experts of several 128-row blocks run as 256-token tiles on clusters of two CTAs
-    (tcgen05.mma.cta_group::2, half of the token rows loaded by each CTA) in a launch of their
-    own; single-block experts keep the 128-token layout.  Against the same call without CTA
-    pairs: the same rows written, values equal up to the order of the stream-K partial sums,
-    status word clear, locks back at zero, twice in a row."""
+    """K = 2048, where tiles of more than 128 tokens run as clusters of two CTAs
+    (tcgen05.mma.cta_group::2, half of the token rows loaded by each CTA, two groups of
+    epilogue warps): `contiguous` with experts of several 128-row blocks (a launch of their
+    own; single-block experts keep the 128-token layout) and `masked` with 256-token tiles.
+    Against the same calls without CTA pairs: the same rows written, values equal up to the
+    order of the stream-K partial sums; against the oracle; status word clear and locks back
+    at zero, twice in a row."""
     import chord_b200
     from chord_b200 import _lib
     from chord_b200.indexed_gemm import default_locks
 
-    case = make_contiguous_case([256, 40, 700, 0, 128, 129, 1], 1024, 1152, seed=77)
+    case = make_contiguous_case([256, 40, 700, 0, 128, 129, 1], 1024, 2048, seed=77)
+    mcase = make_masked_case(5, 256, 512, 2048, 200, seed=78)
+    mcase["masked_m"] = torch.tensor([256, 0, 131, 200, 7], dtype=torch.int32)
     w = chord_b200.pack_w4a16(case["codes"].to(device), case["scale"].to(device))
+    wm = chord_b200.pack_w4a16(mcase["codes"].to(device), mcase["scale"].to(device))
     x2, m_indices = case["x2"].to(device), case["m_indices"].to(device)
-    outs = {}
+    x3, masked_m = mcase["x3"].to(device), mcase["masked_m"].to(device)
+    outs, mouts = {}, {}
     try:
         for pair in (0, 1):
             _lib.set_option("pair", pair)
@@ -239,12 +245,19 @@ def test_cta_pairs_agree_with_single_ctas(device):
                 out = torch.full((x2.size(0), 1024), float("nan"), dtype=torch.bfloat16, device=device)
                 chord_b200.contiguous(x2, w, m_indices, outputs=out)
                 _status_ok(device)
+                mout = torch.full((5 * 256, 512), float("nan"), dtype=torch.bfloat16, device=device)
+                chord_b200.masked(x3, wm, masked_m, 200, outputs=mout)
+                _status_ok(device)
             assert bool((default_locks(device) == 0).all())
-            outs[pair] = out.float().cpu()
+            outs[pair], mouts[pair] = out.float().cpu(), mout.float().cpu()
     finally:
         _lib.set_option("pair", 1)
-    assert torch.equal(torch.isnan(outs[0]), torch.isnan(outs[1]))
-    a, b = outs[0].nan_to_num(), outs[1].nan_to_num()
-    assert float((a == b).float().mean()) >= 0.995
-    assert float((a - b).abs().max()) <= 2.0 ** -6 * float(a.abs().max())
-    _compare(outs[1].to(torch.bfloat16), O.reference_contiguous(case["x2"], case["codes"], case["scale"], case["m_indices"]))
+    for got in (outs, mouts):
+        assert torch.equal(torch.isnan(got[0]), torch.isnan(got[1]))
+        a, b = got[0].nan_to_num(), got[1].nan_to_num()
+        assert float((a == b).float().mean()) >= 0.995
+        assert float((a - b).abs().max()) <= 2.0 ** -6 * float(a.abs().max())
+    _compare(outs[1].to(torch.bfloat16),
+             O.reference_contiguous(case["x2"], case["codes"], case["scale"], case["m_indices"]))
+    ref = O.reference_masked(mcase["x3"], mcase["codes"], mcase["scale"], mcase["masked_m"])
+    _compare(mouts[1].to(torch.bfloat16), ref.reshape(5 * 256, 512))
