@@ -493,6 +493,14 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
   const uint32_t d_bufs = 2u * ni * d_cols <= kTmemCols - d_col0 ? 2u : 1u;
   const int32_t k_iters = (p.k + kBlockK - 1) / kBlockK;
   const bool k_tail_half = (p.k % kBlockK) != 0;  // last stage carries 64 K values only
+  // Consecutive activation rows need one loading thread (warp 2) instead of two gathering
+  // warps, and at most two issuers: warp 0 then feeds both the weight and the scale ring,
+  // the issuers sit in warps 1 and 3, and warps 4-7 are a second group of epilogue warps
+  // taking every other 16-column chunk.  Accumulators of 128 columns and more are
+  // single-buffered, so the tensor core idles while a tile is drained: with K = 2048 the
+  // four-warp drain was a quarter of the time of a two-block tile.
+  const bool tiled_roles = kPair || (p.x_load == kXLoadTiled && ni <= 2u);
+  const uint32_t epi_threads = tiled_roles ? 256u : 128u;
 
   // ------------------------------------------------------------------ setup --
   if (threadIdx.x == 0) {
@@ -518,7 +526,7 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
     }
     for (uint32_t d = 0; d < 2; ++d) {
       ptx::mbar_init(ptx::smem_u32(&sh.dfull[d]), ni);
-      ptx::mbar_init(ptx::smem_u32(&sh.dempty[d]), pair ? 16 : 4);
+      ptx::mbar_init(ptx::smem_u32(&sh.dempty[d]), (tiled_roles ? 8u : 4u) << p.pair);
     }
     sh.abort_flag = 0;
     sh.epilogue_failed = 0;
@@ -646,7 +654,44 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
             static_cast<int32_t>(blockIdx.x >> p.pair));
   Segment seg;
 
-  if (warp == 0 || warp == 1) {
+  if (warp == 0 && tiled_roles) {
+    // ------------------------------ producer of both rings (packed weights, scales) --
+    if (lane == 0) {
+      StageCursor cur;
+      bool ok = true;
+      while (ok && iter.next(seg)) {
+        const TileInfo t = decode_tile(p, sh, seg.tile, rank);
+        if (!t.valid) continue;
+        // to the tile's second weight block: the next 128 rows, or the up rows of a fused gate_up
+        const int32_t block_step = p.fuse_silu ? (p.n >> 1) : kBlockN;
+        int32_t w_row = t.expert * (p.k / 16) + seg.kb * (kBlockK / 16);
+        int32_t s_row = t.expert * (p.k / 32) + seg.kb * (kBlockK / 32);
+        for (int32_t kb = seg.kb; ok && kb < seg.ke; ++kb) {
+          for (int32_t sub = 0; sub < w_per_kb; ++sub) {
+            if (!ptx::mbar_wait(ptx::smem_u32(&sh.wempty[cur.s]), cur.ph ^ 1u, abort_flag)) {
+              ok = false;
+              break;
+            }
+            const uint32_t full = ptx::smem_u32(&sh.wfull[cur.s]);
+            ptx::mbar_arrive_expect_tx(full, kWStageBytes);
+            ptx::tma_load_2d(ptx::smem_u32(smem_w + cur.s * kWStageBytes), &tm_w, full,
+                             2 * (t.n0 + sub * block_step), w_row);
+            ptx::mbar_arrive_expect_tx(full, kSStageBytes);
+            ptx::tma_load_2d(ptx::smem_u32(smem_s + cur.s * kSStageBytes), &tm_s, full,
+                             t.n0 + sub * block_step, s_row);
+            cur.advance(w_stages);
+          }
+          w_row += kBlockK / 16;
+          s_row += kBlockK / 32;
+        }
+      }
+      if (!ok) {
+        sh.abort_flag = 1;
+        if (p.status) atomicOr(p.status, kStatusProducerTimeout);
+      }
+    }
+    __syncwarp();
+  } else if (!tiled_roles && (warp == 0 || warp == 1)) {
     // ------------------------- producers: packed weights (warp 0), scales (warp 1) --
     if (lane == 0) {
       const bool weights = warp == 0;
@@ -685,7 +730,7 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
       }
     }
     __syncwarp();
-  } else if (warp < kFirstIssuerWarp && !(kPair && warp == 3)) {
+  } else if (warp == 2 || (warp == 3 && !tiled_roles)) {
     // ------------------------------------------------ warps 2-3: activations --
     StageCursor cur;
     XSubRing xring;
@@ -908,11 +953,9 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
       sh.abort_flag = 1;
       if (p.status) atomicOr(p.status, kStatusProducerTimeout);
     }
-  } else if (kPair ? warp == 3 : warp < kFirstDequantWarp) {
+  } else if (tiled_roles ? (warp == 1 || warp == 3) : (warp >= kFirstIssuerWarp && warp < kFirstDequantWarp)) {
     // ----------------------------------------------------------- MMA issuers --
-    // (The pair kernel's single issuer sits in warp 3, which has nothing else to do when
-    // the activation rows are consecutive; warps 4-7 are its second epilogue group.)
-    const uint32_t me = kPair ? 0u : warp - kFirstIssuerWarp;
+    const uint32_t me = tiled_roles ? (warp >> 1) : warp - kFirstIssuerWarp;
     if (me < ni && lane == 0 && rank == 0) {
       const uint64_t xdesc0 = ptx::smem_desc_k_sw128(ptx::smem_u32(smem_x));
       const uint64_t xdesc_stage = x_stage_bytes >> 4;  // descriptor address units are 16 bytes
@@ -1241,12 +1284,11 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
     }
   } else {
     // -------------------------------------------------------------- epilogue --
-    // Four warps, one per tensor-memory lane quarter; the pair kernel has a second group
-    // of four (warps 4-7) that takes every other 16-column chunk: its 256-column
-    // accumulator is single-buffered, so the tensor core idles while it is drained.
+    // Four warps, one per tensor-memory lane quarter; with `tiled_roles` a second group of
+    // four (warps 4-7) takes every other 16-column chunk.
     const uint32_t q = warp & 3;
-    constexpr uint32_t kEpiThreads = kPair ? 256u : 128u;
-    const uint32_t egroup = (kPair && warp < kFirstDequantWarp) ? 1u : 0u;
+    const uint32_t kEpiThreads = epi_threads;
+    const uint32_t egroup = warp < kFirstDequantWarp ? 1u : 0u;
     const uint32_t et = threadIdx.x - (egroup ? kFirstIssuerWarp : kFirstEpilogueWarp) * 32;  // 0..127 == TMEM lane
     const uint32_t efill = egroup * 128u + et;  // index among all epilogue threads
     uint32_t segc = 0, it0 = 0;
@@ -1299,7 +1341,7 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
       const int32_t n_sub = t.n0 + sub * kBlockN + static_cast<int32_t>(q) * 32;
       __nv_bfloat16* out_tile = p.out + n_sub;
       const size_t ws_sub = static_cast<size_t>(sub) * ws_block;
-      for (int32_t c0 = static_cast<int32_t>(egroup) * 16; c0 < row_slots; c0 += kPair ? 32 : 16) {
+      for (int32_t c0 = static_cast<int32_t>(egroup) * 16; c0 < row_slots; c0 += tiled_roles ? 32 : 16) {
         float acc[16];
 #pragma unroll
         for (int j = 0; j < 16; ++j) acc[j] = 0.0f;
