@@ -25,7 +25,9 @@ this path).  The same line carries, measured in the same run:
 
 Prints ONE JSON line (rank 0).  `value` is microseconds per step with everything resident
 in HBM; `e2e` is the same step with host buffers (pinned host -> device copies of
-activations and routing, device -> host read of the result) inside the timed region;
+activations and routing, device -> host read of the result: the output rows of the routes
+to local experts, gathered on the device; the other rows of the [routes, N] buffer are
+never written) inside the timed region;
 `roofline` is algorithmic bytes of the two GEMM launches over their CUDA-event time
 against the measured HBM copy bandwidth; `cpu_baseline` / `--impl reference` time the
 reference's CPU torch path (oracle/w4a16_oracle.py) on a bounded sample of the workload.
@@ -167,7 +169,12 @@ class DecodeWorkload:
         self.sorted_host = self.sorted_ids.cpu().pin_memory()
         self.expert_host = self.expert_ids.cpu().pin_memory()
         self.padded_host = self.padded.cpu().pin_memory()
-        self.out_host = torch.empty((routes, HIDDEN), dtype=torch.bfloat16).pin_memory()
+        # The step's result is the rows of the routes to local experts (the only rows of
+        # `out` the kernels write): they are gathered on the device and read back compactly.
+        flat = self.topk.reshape(-1)
+        self.local_routes = torch.nonzero(flat < LOCAL_EXPERTS).reshape(-1).to(device)
+        self.out_local = torch.empty((self.local_routes.numel(), HIDDEN), dtype=torch.bfloat16, device=device)
+        self.out_host = torch.empty((self.local_routes.numel(), HIDDEN), dtype=torch.bfloat16).pin_memory()
         self.bytes_gate_up = traffic_bytes(self.active, 2 * INTER, HIDDEN, batch, self.routed)
         self.bytes_down = traffic_bytes(self.active, HIDDEN, INTER, self.routed, self.routed)
 
@@ -208,7 +215,8 @@ class DecodeWorkload:
         self.expert_ids.copy_(self.expert_host, non_blocking=True)
         self.padded.copy_(self.padded_host, non_blocking=True)
         self.step()
-        self.out_host.copy_(self.out, non_blocking=True)
+        torch.index_select(self.out, 0, self.local_routes, out=self.out_local)
+        self.out_host.copy_(self.out_local, non_blocking=True)
 
     @property
     def h2d_bytes(self):
