@@ -797,13 +797,15 @@ int chord_b200_contiguous(const void* x, const int32_t* packed, const void* scal
   p.locks = locks;
   p.status = status;
   if (two_launches) {
-    // The launches write disjoint rows and use the scratch and the locks one after the
-    // other (the second launch's kernel waits for the first before it touches either).
-    p.run_max = 1;
+    // Each expert's run of 128-row blocks is cut into pairs; the blocks left over (single-
+    // block experts, the last block of an odd run) take 128-token tiles in the first launch,
+    // the pairs 256-token tiles on CTA pairs in the second.  The launches write disjoint
+    // rows and use the scratch and the locks one after the other (the second launch's
+    // kernel waits for the first before it touches either).
+    p.run_part = 1;
     if (int rc = chord::launch_gemm(p, x, packed, scale, num_locks, workspace_bytes, stream)) return rc;
     p.tile_tokens = 256;
-    p.run_min = 2;
-    p.run_max = 0;
+    p.run_part = 2;
   }
   return chord::launch_gemm(p, x, packed, scale, num_locks, workspace_bytes, stream);
 }

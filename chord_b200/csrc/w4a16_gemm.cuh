@@ -117,8 +117,7 @@ struct GemmParams {
   int32_t top_k;        // indexed
   int32_t max_m;        // masked
   int32_t m_blocks;     // contiguous: m / 128
-  int32_t run_min;      // contiguous: only experts whose run of consecutive 128-row blocks has at least
-  int32_t run_max;      //   run_min and (if > 0) at most run_max blocks are computed by this launch
+  int32_t run_part;     // contiguous: 0 = every block; 1 = only the blocks left over when each expert's run of consecutive 128-row blocks is cut into pairs (single-block experts, last block of an odd run); 2 = only the pairs
   int32_t x_box_rows;   // tiled activation loads: rows per TMA box
   int32_t sorted_len;   // indexed: capacity of sorted_ids
   int32_t expert_len;   // indexed: capacity of expert_ids
@@ -604,7 +603,7 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
     __syncthreads();
     if (threadIdx.x == 0) {
       int32_t count = 0;
-      int32_t run_end = 0;  // one past the current expert's run of blocks
+      int32_t run_start = 0, run_end = 0;  // the current expert's run of blocks
       for (int32_t i = 0; i < p.m_blocks;) {
         const int32_t e = static_cast<int32_t>(sh.mtile[i]);
         if (e < 0 || e >= p.num_experts) {
@@ -612,17 +611,19 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
           continue;
         }
         if (i >= run_end) {
-          // A new run: this launch takes it whole or leaves it whole to another launch.
+          run_start = i;
           run_end = i + 1;
           while (run_end < p.m_blocks && static_cast<int32_t>(sh.mtile[run_end]) == e) ++run_end;
-          const int32_t run = run_end - i;
-          if (run < p.run_min || (p.run_max > 0 && run > p.run_max)) {
-            i = run_end;
+        }
+        if (p.run_part != 0) {
+          // Pairs are counted from the start of the run; an odd run leaves its last block.
+          const bool in_pair = i - run_start < ((run_end - run_start) & ~1);
+          if (in_pair != (p.run_part == 2)) {
+            i += in_pair ? 2 : 1;
             continue;
           }
         }
-        const bool merged = p.tile_tokens == 256 && i + 1 < p.m_blocks &&
-                            static_cast<int32_t>(sh.mtile[i + 1]) == e;
+        const bool merged = p.tile_tokens == 256 && i + 1 < run_end;
         sh.tile_rows[count] = merged ? static_cast<uint16_t>(128 + sh.tile_rows[i + 1]) : sh.tile_rows[i];
         sh.mtile[count++] = static_cast<uint32_t>(e) | (static_cast<uint32_t>(i) << 15) |
                             (merged ? 0x80000000u : 0u);

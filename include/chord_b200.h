@@ -62,11 +62,13 @@ const char* chord_b200_version(void);
  *                     rows span two neighbouring 128-row weight blocks, so that an
  *                     activation stage is fetched once per 256 weight rows; 0 one block
  *   "pair"            1 (default) tiles of more than 128 tokens with consecutive activation
- *                     rows and K >= 2048 run on clusters of two CTAs: one tcgen05.mma.cta_group::2 stream
- *                     multiplies two neighbouring 128-row weight blocks (one per CTA) and each
- *                     CTA loads half of the token rows (no multicast); `contiguous` then takes
- *                     two launches, experts of one 128-row block on 128-token tiles and the
- *                     others on 256-token tiles; 0 off
+ *                     rows and K >= 2048 run on clusters of two CTAs: one
+ *                     tcgen05.mma.cta_group::2 stream multiplies two neighbouring 128-row
+ *                     weight blocks (one per CTA) and each CTA loads half of the token rows
+ *                     (no multicast); `contiguous` then takes two launches: each expert's
+ *                     128-row blocks in pairs on 256-token tiles, the blocks left over
+ *                     (single-block experts, the last block of an odd run) on 128-token
+ *                     tiles; 0 off
  *   "decode_kernel"   1 (default) token tiles of at most 32 rows (indexed, masked) run
  *                     the warpgroup-per-worker kernel; 0 always the general kernel
  *   "max_stages"      0 as many shared-memory stages as fit (default), else a cap
