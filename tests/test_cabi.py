@@ -51,8 +51,8 @@ def test_block_m_queries(native_lib):
         bm = native_lib.chord_b200_indexed_block_m(4096, 7168, 48, routed)
         assert bm >= prev
         prev = bm
-    assert [native_lib.chord_b200_masked_tile_m(m) for m in (1, 8, 16, 17, 32, 128, 129, 10**4)] == \
-        [16, 16, 16, 32, 32, 128, 256, 256]
+    assert [native_lib.chord_b200_masked_tile_m(m) for m in (1, 8, 9, 20, 21, 48, 49, 144, 145, 10**4)] == \
+        [16, 16, 32, 32, 64, 64, 128, 128, 256, 256]
 
 
 def _segments(lib, tiles, k, grid, cta):
