@@ -219,7 +219,7 @@ def test_contiguous_matches_the_references_own_test_vectors(device, name):
 
 
 def test_cta_pairs_agree_with_single_ctas(device):
-    """K = 2048, where tiles of more than 128 tokens run as clusters of two CTAs
+    """K >= 2048, where tiles of more than 128 tokens run as clusters of two CTAs
     (tcgen05.mma.cta_group::2, half of the token rows loaded by each CTA, two groups of
     epilogue warps): `contiguous` with experts of several 128-row blocks (a launch of their
     own; single-block experts keep the 128-token layout) and `masked` with 256-token tiles.
@@ -230,7 +230,7 @@ def test_cta_pairs_agree_with_single_ctas(device):
     from chord_b200 import _lib
     from chord_b200.indexed_gemm import default_locks
 
-    case = make_contiguous_case([256, 40, 700, 0, 128, 129, 1], 1024, 2048, seed=77)
+    case = make_contiguous_case([256, 40, 700, 0, 128, 129, 1], 1024, 2368, seed=77)  # last K stage half-filled
     mcase = make_masked_case(5, 256, 512, 2048, 200, seed=78)
     mcase["masked_m"] = torch.tensor([256, 0, 131, 200, 7], dtype=torch.int32)
     w = chord_b200.pack_w4a16(case["codes"].to(device), case["scale"].to(device))
