@@ -37,6 +37,8 @@ SIGNATURES = {
                                   _ptr, _i64, _ptr, _i64, _i64, _i64, _i64, _i64, _i64, _ptr]),
     "chord_b200_indexed_rows": (_int, [_ptr, _ptr, _ptr, _ptr, _i64, _ptr, _i64, _ptr, _ptr, _ptr, _i64,
                                        _ptr, _i64, _ptr, _i64, _i64, _i64, _i64, _i64, _i64, _ptr]),
+    "chord_b200_indexed_slots": (_int, [_ptr, _ptr, _ptr, _ptr, _i64, _ptr, _i64, _ptr, _ptr, _ptr, _ptr, _i64,
+                                        _ptr, _i64, _ptr, _i64, _i64, _i64, _i64, _i64, _int, _ptr]),
     "chord_b200_indexed_gate_up_silu": (_int, [_ptr, _ptr, _ptr, _ptr, _i64, _ptr, _i64, _ptr, _ptr, _ptr,
                                                _i64, _ptr, _i64, _ptr, _i64, _i64, _i64, _i64, _i64, _i64,
                                                _ptr]),
@@ -56,7 +58,7 @@ SIGNATURES = {
     "chord_b200_ep_state_bytes": (_i64, []),
     "chord_b200_ep_plan": (_int, [_ptr, _i64, _i64, _i64, _i64, _ptr, _ptr, _i64, _ptr]),
     "chord_b200_ep_dispatch": (_int, [_ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _i64, _i64, _ptr, _ptr,
-                                      _ptr, _ptr, _i64, _i64, _ptr]),
+                                      _ptr, _ptr, _i64, _i64, _i64, _ptr]),
     "chord_b200_ep_align": (_int, [_ptr, _ptr, _i64, _i64, _i64, _i64, _i64, _ptr, _i64, _ptr, _i64, _ptr,
                                    _ptr, _ptr, _i64, _i64, _ptr, _i64, _ptr]),
     "chord_b200_ep_combine_signal": (_int, [_ptr, _i64, _i64, _i64, _ptr]),

@@ -362,7 +362,9 @@ int launch_gemm(GemmParams p, const void* x, const int32_t* packed, const void* 
   // Large routing blocks: slot-ordered copy of the activations behind the stream-K
   // partials, if the caller's workspace has room for it (chord_b200_indexed_workspace_bytes).
   __nv_bfloat16* gathered = nullptr;
-  if (p.mode == kModeIndexed && pregather_applies(p.mma_n) && p.sorted_len > 0) {
+  if (p.mode == kModeIndexed && p.slot_ordered) {
+    p.x_load = kXLoadTiled;
+  } else if (p.mode == kModeIndexed && pregather_applies(p.mma_n) && p.sorted_len > 0) {
     const int64_t offset = stream_k_bytes(grid, p.mma_n);
     const int64_t bytes = static_cast<int64_t>(p.sorted_len) * p.k * 2;
     if (workspace_bytes >= offset + bytes) {
@@ -646,7 +648,7 @@ static int indexed_launch(const void* x, const int32_t* packed, const void* scal
                           void* const* out_rows, int32_t* locks, int64_t num_locks, void* workspace,
                           int64_t workspace_bytes, int32_t* status, int64_t m, int64_t n, int64_t k,
                           int64_t num_experts, int64_t top_k, int64_t block_m, void* stream,
-                          int fuse_silu = 0) {
+                          int fuse_silu = 0, int slot_ordered = 0) {
   CHORD_REQUIRE(m > 0, "inputs must be non-empty, got m=%lld", static_cast<long long>(m));
   CHORD_REQUIRE(top_k > 0, "top_k must be positive, got %lld", static_cast<long long>(top_k));
   CHORD_REQUIRE(block_m > 0 && block_m % 8 == 0 && block_m <= chord::kMaxTileTokens,
@@ -674,10 +676,24 @@ static int indexed_launch(const void* x, const int32_t* packed, const void* scal
   p.out = static_cast<__nv_bfloat16*>(out);
   p.out_row_ptr = out_rows;
   p.fuse_silu = fuse_silu;
+  p.slot_ordered = slot_ordered;
   p.workspace = static_cast<float*>(workspace);
   p.locks = locks;
   p.status = status;
   return chord::launch_gemm(p, x, packed, scale, num_locks, workspace_bytes, stream);
+}
+
+int chord_b200_indexed_slots(const void* x, const int32_t* packed, const void* scale,
+                             const int32_t* sorted_ids, int64_t sorted_len, const int32_t* expert_ids,
+                             int64_t expert_len, const int32_t* num_tokens_padded, void* out,
+                             void* const* out_rows, int32_t* locks, int64_t num_locks, void* workspace,
+                             int64_t workspace_bytes, int32_t* status, int64_t m, int64_t n, int64_t k,
+                             int64_t num_experts, int64_t block_m, int fuse_silu, void* stream) {
+  CHORD_REQUIRE(out != nullptr || out_rows != nullptr, "null output pointer and null row-address table");
+  CHORD_REQUIRE(sorted_len <= m, "slot-ordered rows: x must hold a row for every routing slot");
+  return indexed_launch(x, packed, scale, sorted_ids, sorted_len, expert_ids, expert_len,
+                        num_tokens_padded, out, out_rows, locks, num_locks, workspace, workspace_bytes,
+                        status, m, n, k, num_experts, 1, block_m, stream, fuse_silu != 0, 1);
 }
 
 int chord_b200_indexed(const void* x, const int32_t* packed, const void* scale,

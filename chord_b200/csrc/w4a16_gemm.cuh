@@ -130,6 +130,7 @@ struct GemmParams {
   int32_t pair;         // 1 = launched as clusters of two CTAs: a tile is two neighbouring 128-row weight blocks, one per CTA, multiplied by one tcgen05.mma.cta_group::2 stream; each CTA loads half of the tile's token rows
   int32_t a_stages;     // depth of the TMEM A ring; accumulators start at column 64 * a_stages
   int32_t num_locks;
+  int32_t slot_ordered; // host side only (indexed): row s of x is the row of routing slot s, so the rows load as consecutive boxes without a copy
   int32_t pdl;          // host side only: launch with the programmatic stream-serialization attribute
   int32_t lock_spins;   // polls (64 ns apart) a stream-K owner spends on its lock word before it gives up
   const int32_t* sorted_ids;

@@ -161,7 +161,7 @@ def _align(value: int, unit: int = 256) -> int:
 class ExchangeLayout:
     """Byte offsets of one rank's exchange buffers inside its peer-visible allocation."""
 
-    capacity: int        # rows the receive buffers hold: every route of every rank
+    capacity: int        # slots of the receive buffers: every route of every rank, each local expert's rows padded to whole routing blocks
     routed_rows: int     # rows of this rank's result tensor (tokens * top_k)
     hidden_in: int
     hidden_out: int
@@ -173,12 +173,14 @@ class ExchangeLayout:
 
     @staticmethod
     def build(world: int, max_tokens: int, top_k: int, hidden_in: int, hidden_out: int,
-              state_bytes: int) -> "ExchangeLayout":
+              state_bytes: int, experts_per_rank: int = 0, block_m: int = 1) -> "ExchangeLayout":
         routed_rows = max_tokens * top_k
-        capacity = world * routed_rows      # the worst case: every route lands on one rank
+        # the worst case: every route lands on one rank, every expert's last block nearly empty
+        worst = world * routed_rows + experts_per_rank * (block_m - 1)
+        capacity = (worst + block_m - 1) // block_m * block_m
         state = 0
         recv_tag = _align(state + state_bytes)
-        recv_x = _align(recv_tag + 2 * capacity * 4)
+        recv_x = _align(recv_tag + capacity * 4)
         routed = _align(recv_x + capacity * hidden_in * 2)
         total = _align(routed + routed_rows * hidden_out * 2)
         return ExchangeLayout(capacity, routed_rows, hidden_in, hidden_out, state, recv_tag, recv_x,
@@ -241,6 +243,18 @@ class ExpertParallelLayer:
     the tokens directly.
     """
 
+    @staticmethod
+    def exchange_layout(w13, w2, *, world: int, max_tokens: int, top_k: int) -> "ExchangeLayout":
+        """Layout of one rank's peer-visible buffers (what a fabric has to allocate): the
+        receive buffers are sized in routing blocks of the block size the local GEMMs use."""
+        from . import _lib
+        from .indexed_gemm import select_block_m
+
+        # expected rows per rank if the routes spread evenly: sizes the routing blocks
+        block_m = select_block_m(w13.n, w13.k, w13.num_experts, max_tokens * top_k)
+        return ExchangeLayout.build(world, max_tokens, top_k, w13.k, w2.n,
+                                    _lib.load().chord_b200_ep_state_bytes(), w13.num_experts, block_m)
+
     def __init__(self, w13, w2, *, num_experts_total: int, max_tokens: int, top_k: int,
                  fabric=None, group=None):
         from . import _lib
@@ -253,8 +267,8 @@ class ExpertParallelLayer:
         if w2.k * 2 != w13.n:
             raise ValueError(f"w13 has {w13.n} rows, w2 reduces over {w2.k}: expected n13 == 2 * k2")
         if fabric is None and group is not None and dist.get_world_size(group) > 1:
-            layout = ExchangeLayout.build(dist.get_world_size(group), max_tokens, top_k, self.hidden_in,
-                                          self.hidden_out, self.lib.chord_b200_ep_state_bytes())
+            layout = self.exchange_layout(w13, w2, world=dist.get_world_size(group), max_tokens=max_tokens,
+                                          top_k=top_k)
             fabric = SymmetricFabric(layout.total, group, self.device)
         self.fabric = fabric
         self.world = fabric.world if fabric is not None else 1
@@ -269,8 +283,7 @@ class ExpertParallelLayer:
         self.spans = None          # optional: list that receives (name, start event, end event)
         if self.world == 1:
             return
-        self.layout = ExchangeLayout.build(self.world, max_tokens, top_k, self.hidden_in, self.hidden_out,
-                                           self.lib.chord_b200_ep_state_bytes())
+        self.layout = self.exchange_layout(w13, w2, world=self.world, max_tokens=max_tokens, top_k=top_k)
         lay, dev = self.layout, self.device
         if fabric.buffer.numel() < lay.total:
             raise ValueError("the fabric's allocation is smaller than the exchange layout")
@@ -282,24 +295,25 @@ class ExpertParallelLayer:
         self.peer_recv_x, self.peer_routed = table(lay.recv_x), table(lay.routed)
         buf = fabric.buffer
         self.state = buf[lay.state:lay.recv_tag]
-        self.recv_tag = buf[lay.recv_tag:lay.recv_tag + 2 * lay.capacity * 4].view(torch.int32)
+        self.recv_tag = buf[lay.recv_tag:lay.recv_tag + lay.capacity * 4].view(torch.int32)
         self.recv_x = buf[lay.recv_x:lay.recv_x + lay.capacity * self.hidden_in * 2].view(
             torch.bfloat16).view(lay.capacity, self.hidden_in)
         self.routed = buf[lay.routed:lay.routed + lay.routed_rows * self.hidden_out * 2].view(
             torch.bfloat16).view(lay.routed_rows, self.hidden_out)
-        # expected rows per rank if the routes spread evenly: sizes the routing blocks
         from .indexed_gemm import select_block_m
 
         self.block_m = select_block_m(w13.n, w13.k, self.experts_per_rank, lay.routed_rows)
-        worst = lay.capacity + self.experts_per_rank * (self.block_m - 1)
-        blocks = worst // self.block_m
-        self.sorted_ids = torch.empty(blocks * self.block_m, dtype=torch.int32, device=dev)
+        blocks = lay.capacity // self.block_m
+        self.sorted_ids = torch.empty(lay.capacity, dtype=torch.int32, device=dev)
         self.expert_ids = torch.empty(blocks, dtype=torch.int32, device=dev)
         self.padded = torch.zeros(1, dtype=torch.int32, device=dev)
         self.recv_count = torch.zeros(1, dtype=torch.int32, device=dev)
         self.send_pos = torch.empty(lay.routed_rows, dtype=torch.int32, device=dev)
         self.row_ptr = torch.zeros(lay.capacity, dtype=torch.int64, device=dev)
         self.hidden = torch.empty((lay.capacity, self.inter2 // 2), dtype=torch.bfloat16, device=dev)
+        fused = bool(self.lib.chord_b200_gate_up_silu_supported(w13.n, w13.k, self.block_m))
+        self.gate_up = None if fused else torch.empty((lay.capacity, self.inter2), dtype=torch.bfloat16,
+                                                      device=dev)
 
     # -- helpers ---------------------------------------------------------------------
     def _stream(self):
@@ -355,12 +369,12 @@ class ExpertParallelLayer:
             self._x.data_ptr(), self._topk.data_ptr(), self.send_pos.data_ptr(), self._routes, self.top_k,
             self.hidden_in, self.experts_per_rank, self.world, self.rank, self.state.data_ptr(),
             self.peer_state.data_ptr(), self.peer_recv_x.data_ptr(), self.peer_recv_tag.data_ptr(),
-            self.layout.capacity, self.epoch, self._stream()))
+            self.layout.capacity, self.block_m, self.epoch, self._stream()))
         self._end(span)
 
     def local_experts(self) -> None:
         from . import _lib
-        from .indexed_gemm import gemm_scratch, indexed_gate_up_silu, status_word
+        from .indexed_gemm import gemm_scratch, status_word
 
         lay = self.layout
         span = self._span("align")
@@ -372,19 +386,31 @@ class ExpertParallelLayer:
             self.row_ptr.data_ptr(), self.epoch, self._stream()))
         self._end(span)
         span = self._span("experts")
-        routing = (self.sorted_ids, self.expert_ids, self.padded)
-        indexed_gate_up_silu(self.recv_x, self.w13, *routing, 1, locks=self.locks, outputs=self.hidden,
-                             block_m=self.block_m)
-        # down: every result row goes straight to the result tensor of the rank it came from
-        locks, workspace, ws_bytes = gemm_scratch(self.device, self.block_m, self.locks,
-                                                  self.sorted_ids.numel(), self.w2.k)
-        _lib.check(self.lib.chord_b200_indexed_rows(
-            self.hidden.data_ptr(), self.w2.packed.data_ptr(), self.w2.scale.data_ptr(),
-            self.sorted_ids.data_ptr(), self.sorted_ids.numel(), self.expert_ids.data_ptr(),
-            self.expert_ids.numel(), self.padded.data_ptr(), self.row_ptr.data_ptr(),
-            locks.data_ptr(), locks.numel(), workspace.data_ptr(), ws_bytes,
-            status_word(self.device).data_ptr(), lay.capacity, self.w2.n, self.w2.k,
-            self.experts_per_rank, 1, self.block_m, self._stream()))
+        # The rows arrived in routing-slot order: both GEMMs load them where they are.
+        # gate_up with SiLU*mul in the epilogue (a separate SiLU*mul where that is not
+        # supported), then down, whose epilogue stores every result row straight into the
+        # result tensor of the rank the token came from.
+        from .fused_ops import silu_mul
+
+        status = status_word(self.device).data_ptr()
+
+        def slots_gemm(weight, x, out_ptr, rows_ptr, fuse):
+            locks, workspace, ws_bytes = gemm_scratch(self.device, self.block_m, self.locks,
+                                                      self.sorted_ids.numel(), weight.k)
+            _lib.check(self.lib.chord_b200_indexed_slots(
+                x.data_ptr(), weight.packed.data_ptr(), weight.scale.data_ptr(),
+                self.sorted_ids.data_ptr(), self.sorted_ids.numel(), self.expert_ids.data_ptr(),
+                self.expert_ids.numel(), self.padded.data_ptr(), out_ptr, rows_ptr,
+                locks.data_ptr(), locks.numel(), workspace.data_ptr(), ws_bytes, status, lay.capacity,
+                weight.n, weight.k, self.experts_per_rank, self.block_m, fuse, self._stream()))
+
+        if self.gate_up is None:
+            slots_gemm(self.w13, self.recv_x, self.hidden.data_ptr(), 0, 1)
+        else:
+            slots_gemm(self.w13, self.recv_x, self.gate_up.data_ptr(), 0, 0)
+            silu_mul(self.gate_up, sorted_ids=self.sorted_ids, num_tokens_padded=self.padded,
+                     outputs=self.hidden)
+        slots_gemm(self.w2, self.hidden, 0, self.row_ptr.data_ptr(), 0)
         _lib.check(self.lib.chord_b200_ep_combine_signal(
             self.peer_state.data_ptr(), self.world, self.rank, self.epoch, self._stream()))
         self._end(span)

@@ -196,6 +196,23 @@ int chord_b200_indexed_rows(const void* x, const int32_t* packed, const void* sc
                             int32_t* status, int64_t m, int64_t n, int64_t k, int64_t num_experts,
                             int64_t top_k, int64_t block_m, void* stream);
 
+/* ---- indexed GEMM over rows that are already in routing-slot order ----------------
+ * No counterpart in the reference.  Same operation as chord_b200_indexed with top_k = 1,
+ * for a caller that has placed the activation rows where the routing puts them: row s of
+ * x (bf16 [m, k], m >= sorted_len) belongs to slot s, and sorted_ids[s] is s for a slot that
+ * holds a row and any value >= m for padding.  The kernel then loads the rows of a block
+ * as consecutive TMA boxes; nothing is gathered or copied.  The result of slot s goes to
+ * out + s * n (out != null), or to the row whose address is out_rows[s] (out == null, as
+ * chord_b200_indexed_rows); with fuse_silu != 0, w is a gate_up projection and out receives
+ * silu(gate) * up, [m, n / 2] (as chord_b200_indexed_gate_up_silu, same support rules).
+ * The expert-parallel layer receives its rows in this order (chord_b200_ep_dispatch). */
+int chord_b200_indexed_slots(const void* x, const int32_t* packed, const void* scale,
+                             const int32_t* sorted_ids, int64_t sorted_len, const int32_t* expert_ids,
+                             int64_t expert_len, const int32_t* num_tokens_padded, void* out,
+                             void* const* out_rows, int32_t* locks, int64_t num_locks, void* workspace,
+                             int64_t workspace_bytes, int32_t* status, int64_t m, int64_t n, int64_t k,
+                             int64_t num_experts, int64_t block_m, int fuse_silu, void* stream);
+
 /* ---- indexed GEMM without a workspace argument ---------------------------------
  * No counterpart in the reference (its launcher always takes the stream-K scratch
  * from torch's allocator).  Same operation and arguments as chord_b200_indexed, but
@@ -292,30 +309,35 @@ int chord_b200_moe_align_block_size(const int32_t* topk_ids, int64_t numel, int6
  * (symmetric memory, CUDA IPC) and passes device arrays of the `world` addresses as this
  * process sees them:
  *   peer_state     exchange state of chord_b200_ep_state_bytes() bytes, zeroed once
- *   peer_recv_x    bf16 [capacity, hidden]: routed activation rows arriving at the owner
- *   peer_recv_tag  int32 [2, capacity]: local expert of each arriving row, then
- *                  source rank << 24 | route
+ *   peer_recv_x    bf16 [capacity, hidden]: routed activation rows arriving at the owner,
+ *                  already in routing order: expert after expert, each expert's rows padded
+ *                  to whole blocks of block_m slots (capacity = a multiple of block_m that
+ *                  covers every route of every rank plus block_m - 1 slots per local expert)
+ *   peer_recv_tag  int32 [capacity]: source rank << 24 | route of the row in each slot
  *   peer_routed    bf16 [routed_rows_per_rank, hidden]: result rows, route order
  * `epoch` is a counter every rank advances by one per layer call (1, 2, ...): flags
  * carry it, nothing is reset between calls.  The kernels use plain peer loads and
  * stores, no TMA and no multicast.  Every cross-GPU wait is bounded (about five
  * seconds); a wait that runs out ORs a bit into the `status` word at the end of the
  * state (256 counts, 512 rows, 1024 results, 2048 receive buffer too small) and the
- * kernel carries on with incomplete data instead of hanging.
+ * kernel carries on with incomplete data instead of hanging.  At most 1024 experts over
+ * all ranks.
  * One layer call, all on one stream:
  *   chord_b200_ep_plan      send_pos[i] = position of route i among this rank's routes to
- *                           the same destination (-1 for an expert outside all ranks);
- *                           publishes the per-destination counts to every peer
- *   chord_b200_ep_dispatch  waits for all counts, copies every route's row and tag into
- *                           its owner's receive buffers (rows ordered by source rank,
- *                           then route), flags every peer
- *   chord_b200_ep_align     on the owner: waits for all rows; recv_count = rows received;
- *                           sorted_ids / expert_ids / num_tokens_padded over the received
- *                           expert tags as chord_b200_moe_align_block_size produces them
- *                           (sentinel = capacity); row_ptr[i] = address in the source
- *                           rank's peer_routed of the row that receives row i's result
- *   (gate_up = chord_b200_indexed on recv_x with m = capacity, top_k = 1; SiLU*mul;
- *    down = chord_b200_indexed_rows with out_rows = row_ptr)
+ *                           the same expert (-1 for an expert outside all ranks);
+ *                           publishes the per-expert counts to every peer
+ *   chord_b200_ep_dispatch  waits for all counts, derives the first slot of this rank's rows
+ *                           of every expert in its owner's buffers (inside an expert: source
+ *                           rank after source rank), copies every route's row and tag
+ *                           there, flags every peer
+ *   chord_b200_ep_align     on the owner: waits for all rows; recv_count =
+ *                           *num_tokens_padded = slots in use; sorted_ids[s] = s for a slot
+ *                           that holds a row, capacity for padding; expert_ids per block;
+ *                           row_ptr[s] = address in the source rank's peer_routed of the row
+ *                           that receives slot s's result
+ *   (gate_up + SiLU*mul = chord_b200_indexed_slots on recv_x with m = capacity and
+ *    fuse_silu = 1; down = chord_b200_indexed_slots with out_rows = row_ptr: the rows are
+ *    loaded where they landed, nothing is copied into slot order)
  *   chord_b200_ep_combine_signal   flags every peer: this owner's results are stored
  *   chord_b200_ep_combine_wait     returns (stream-ordered) once every owner has flagged */
 int64_t chord_b200_ep_state_bytes(void);
@@ -325,7 +347,8 @@ int chord_b200_ep_plan(const int32_t* topk_ids, int64_t routes, int64_t experts_
 int chord_b200_ep_dispatch(const void* x, const int32_t* topk_ids, const int32_t* send_pos, int64_t routes,
                            int64_t top_k, int64_t hidden, int64_t experts_per_rank, int64_t world,
                            int64_t rank, void* state, void* const* peer_state, void* const* peer_recv_x,
-                           void* const* peer_recv_tag, int64_t capacity, int64_t epoch, void* stream);
+                           void* const* peer_recv_tag, int64_t capacity, int64_t block_m, int64_t epoch,
+                           void* stream);
 int chord_b200_ep_align(void* state, const int32_t* recv_tag, int64_t capacity, int64_t world, int64_t rank,
                         int64_t num_local_experts, int64_t block_m, int32_t* sorted_ids, int64_t sorted_cap,
                         int32_t* expert_ids, int64_t expert_cap, int32_t* num_tokens_padded,

@@ -107,14 +107,15 @@ def test_single_rank_layer_needs_no_process_group():
 
 def test_exchange_layout_covers_the_worst_case():
     """Buffer layout of the peer-memory exchange: the receive buffers hold every route of
-    every rank (the worst case: all of them land on one rank), regions are 256-byte
-    aligned and do not overlap."""
+    every rank (the worst case: all of them land on one rank) with every local expert's
+    rows padded to whole routing blocks, regions are 256-byte aligned and do not overlap."""
     from chord_b200.ep import ExchangeLayout
 
     lay = ExchangeLayout.build(world=8, max_tokens=512, top_k=8, hidden_in=7168, hidden_out=7168,
-                               state_bytes=17160)
-    assert lay.routed_rows == 4096 and lay.capacity == 8 * 4096
-    regions = [(lay.state, 17160), (lay.recv_tag, 2 * lay.capacity * 4),
+                               state_bytes=17160, experts_per_rank=48, block_m=128)
+    assert lay.routed_rows == 4096
+    assert lay.capacity % 128 == 0 and 0 <= lay.capacity - (8 * 4096 + 48 * 127) < 128
+    regions = [(lay.state, 17160), (lay.recv_tag, lay.capacity * 4),
                (lay.recv_x, lay.capacity * 7168 * 2), (lay.routed, lay.routed_rows * 7168 * 2)]
     end = 0
     for start, size in regions:

@@ -81,13 +81,15 @@ def test_single_gpu_layer_matches_oracle(device):
     assert O.max_abs_rel(got, ref) <= 2e-2      # two GEMMs and an activation in BF16
 
 
-@pytest.mark.parametrize("world,tokens,top_k", [(2, 24, 2), (4, 33, 4)])
+@pytest.mark.parametrize("world,tokens,top_k", [(2, 24, 2), (4, 33, 4), (2, 96, 4), (2, 300, 4)])
 def test_peer_memory_exchange_with_all_ranks_on_one_gpu(device, world, tokens, top_k):
     """The expert-parallel layer's own kernels (plan, dispatch by peer stores, receive-side
     alignment, down projection storing into the source rank's result tensor, flags) with
     every rank living on this one GPU: each step is run for all ranks before the next, so
     no kernel waits for a later launch.  Every rank's routed outputs must equal the
-    oracle's gate_up -> SiLU*mul -> down on the owning expert's weights."""
+    oracle's gate_up -> SiLU*mul -> down on the owning expert's weights.  The rows arrive
+    in routing-slot order and the GEMMs load them in place; the cases cover routing blocks
+    of 16 to 256 rows (both GEMM kernels)."""
     import chord_b200
     from chord_b200 import ep
 
@@ -95,15 +97,17 @@ def test_peer_memory_exchange_with_all_ranks_on_one_gpu(device, world, tokens, t
     per_rank = experts_total // world
     codes13, scale13 = make_weights(experts_total, 2 * inter, hidden, seed=61)
     codes2, scale2 = make_weights(experts_total, hidden, inter, seed=62)
-    lib_state = chord_b200._lib.load().chord_b200_ep_state_bytes()
-    layout = ep.ExchangeLayout.build(world, tokens, top_k, hidden, hidden, lib_state)
+    weights = []
+    for r in range(world):
+        lo, hi = r * per_rank, (r + 1) * per_rank
+        weights.append((chord_b200.pack_w4a16(codes13[lo:hi].to(device), scale13[lo:hi].to(device)),
+                        chord_b200.pack_w4a16(codes2[lo:hi].to(device), scale2[lo:hi].to(device))))
+    layout = ep.ExpertParallelLayer.exchange_layout(*weights[0], world=world, max_tokens=tokens, top_k=top_k)
     fabric = ep.LocalFabric(layout.total, world, device)
     layers, xs, topks = [], [], []
     g = torch.Generator().manual_seed(63)
     for r in range(world):
-        lo, hi = r * per_rank, (r + 1) * per_rank
-        w13 = chord_b200.pack_w4a16(codes13[lo:hi].to(device), scale13[lo:hi].to(device))
-        w2 = chord_b200.pack_w4a16(codes2[lo:hi].to(device), scale2[lo:hi].to(device))
+        w13, w2 = weights[r]
         layers.append(ep.ExpertParallelLayer(w13, w2, num_experts_total=experts_total, max_tokens=tokens,
                                              top_k=top_k, fabric=fabric.view(r)))
         n_tok = tokens - r                       # ranks bring different token counts
