@@ -169,3 +169,51 @@ def test_gate_up_with_fused_silu_mul(device, experts, n, k, m, top_k, block_m):
     assert O.max_abs_rel(got, want) <= 1.5e-2    # BF16 output of a product of two GEMM results
     for other in outs[1:]:
         assert torch.equal(other.view(torch.int16), outs[0].view(torch.int16))
+
+
+@pytest.mark.parametrize("experts,n,k,m,block_m,fuse", [
+    (6, 1024, 640, 500, 128, 0), (6, 1024, 640, 500, 128, 1), (4, 512, 2304, 700, 256, 0),
+    (8, 512, 512, 40, 16, 0), (8, 512, 512, 40, 16, 1), (4, 512, 384, 150, 64, 1),
+])
+def test_rows_already_in_slot_order(device, experts, n, k, m, block_m, fuse):
+    """`chord_b200_indexed_slots`: the caller has placed row s of the activations at routing
+    slot s (ids are the slots themselves, padding slots hold garbage and a sentinel id).
+    The rows are loaded in place; the results must be those of `indexed` /
+    `indexed_gate_up_silu` on the original rows, row for row, bit for bit (same kernels,
+    same tiles; only the way the rows reach shared memory differs)."""
+    import chord_b200
+    from chord_b200 import _lib
+    from chord_b200.indexed_gemm import gemm_scratch, status_word
+    from tests.cases import make_indexed_case
+
+    case = make_indexed_case(num_experts=experts, n=n, k=k, m=m, top_k=1, block_m=block_m, seed=300 + m)
+    w = chord_b200.pack_w4a16(case["codes"].to(device), case["scale"].to(device))
+    sorted_ids = case["sorted_ids"].to(device)
+    routing = (sorted_ids, case["expert_ids"].to(device), case["num_tokens_padded"].to(device).reshape(1))
+    x = case["x"].to(device)
+    width = n // 2 if fuse else n
+    want = torch.full((m, width), float("nan"), dtype=torch.bfloat16, device=device)
+    if fuse:
+        chord_b200.indexed_gate_up_silu(x, w, *routing, 1, outputs=want, block_m=block_m)
+    else:
+        chord_b200.indexed(x, w, *routing, 1, outputs=want, block_m=block_m)
+    # slot-ordered copy of the rows: garbage (NaN) in the padding slots
+    slots = sorted_ids.numel()
+    valid = sorted_ids < m
+    x_slots = torch.full((slots, k), float("nan"), dtype=torch.bfloat16, device=device)
+    x_slots[valid] = x[sorted_ids[valid].long()]
+    slot_ids = torch.where(valid, torch.arange(slots, device=device, dtype=torch.int32),
+                           torch.full_like(sorted_ids, slots))
+    got = torch.full((slots, width), float("nan"), dtype=torch.bfloat16, device=device)
+    lib = _lib.load()
+    locks, workspace, ws_bytes = gemm_scratch(device, block_m, None, slots, k)
+    _lib.check(lib.chord_b200_indexed_slots(
+        x_slots.data_ptr(), w.packed.data_ptr(), w.scale.data_ptr(), slot_ids.data_ptr(), slots,
+        routing[1].data_ptr(), routing[1].numel(), routing[2].data_ptr(), got.data_ptr(), 0,
+        locks.data_ptr(), locks.numel(), workspace.data_ptr(), ws_bytes, status_word(device).data_ptr(),
+        slots, n, k, experts, block_m, fuse, _lib.stream_handle(device)))
+    torch.cuda.synchronize()
+    assert int(status_word(device).item()) == 0
+    # exactly the slots that hold a row are written, with the values of the original call
+    assert torch.equal(~torch.isnan(got.float()).any(dim=1), valid)
+    assert torch.equal(got[valid], want[sorted_ids[valid].long()])
