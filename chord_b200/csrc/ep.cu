@@ -35,7 +35,6 @@
 
 #include "../../include/chord_b200.h"
 #include "common.h"
-#include "routing.cuh"
 
 namespace chord {
 namespace {
