@@ -261,3 +261,28 @@ def test_cta_pairs_agree_with_single_ctas(device):
              O.reference_contiguous(case["x2"], case["codes"], case["scale"], case["m_indices"]))
     ref = O.reference_masked(mcase["x3"], mcase["codes"], mcase["scale"], mcase["masked_m"])
     _compare(mouts[1].to(torch.bfloat16), ref.reshape(5 * 256, 512))
+
+
+def test_programmatic_dependent_launch_does_not_change_grouped_results(device):
+    """`enable_pdl=True` on `contiguous` (two launches, the second on clusters of two CTAs)
+    and `masked` (256-token tiles on clusters): the launch attribute only lets a kernel's
+    set-up overlap its predecessor's tail, so the outputs are bit-equal to plain launches."""
+    import chord_b200
+
+    case = make_contiguous_case([256, 40, 700, 0, 128, 129, 1], 1024, 2368, seed=77)
+    mcase = make_masked_case(5, 256, 512, 2048, 200, seed=78)
+    w = chord_b200.pack_w4a16(case["codes"].to(device), case["scale"].to(device))
+    wm = chord_b200.pack_w4a16(mcase["codes"].to(device), mcase["scale"].to(device))
+    x2, m_indices = case["x2"].to(device), case["m_indices"].to(device)
+    x3, masked_m = mcase["x3"].to(device), mcase["masked_m"].to(device)
+    results = {}
+    for pdl in (False, True):
+        for _ in range(3):          # back to back, so that a launch does follow a running kernel
+            out = torch.full((x2.size(0), 1024), float("nan"), dtype=torch.bfloat16, device=device)
+            chord_b200.contiguous(x2, w, m_indices, outputs=out, enable_pdl=pdl)
+            mout = torch.full((5 * 256, 512), float("nan"), dtype=torch.bfloat16, device=device)
+            chord_b200.masked(x3, wm, masked_m, 200, outputs=mout, enable_pdl=pdl)
+        _status_ok(device)
+        results[pdl] = (out, mout)
+    for plain, overlapped in zip(results[False], results[True]):
+        assert torch.equal(plain.view(torch.int16), overlapped.view(torch.int16))
